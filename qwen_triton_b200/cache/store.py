@@ -2,7 +2,8 @@
 
 Layers whose mixers ask for the same thing (kv heads, head size, all keys or a window of them)
 form a *group* with storage of its own: one key and one value pool
-``[entries, pages, kv_heads, page_tokens, head_dim]`` shared by the group's entries, one page list
+``[entries, pages, kv_heads, page_tokens, head_dim]`` (values with their own head size where a mixer says so)
+shared by the group's entries, one page list
 per sequence for the whole group.  Beside the pools each mixer that asks for it has a fixed-size
 state block per slot, ``[num_slots + 1, *shape]`` (the last row is a spare for padded rows), zeroed when a slot is handed out; the architecture
 built here asks for none, and the plumbing is exercised by a toy mixer in the tests.
@@ -23,7 +24,7 @@ class CacheView:
 
     group: int | None = None          # index of its kv group (None: no keys/values)
     k: torch.Tensor | None = None     # [pages, kv_heads, page_tokens, head_dim]
-    v: torch.Tensor | None = None
+    v: torch.Tensor | None = None     # [pages, kv_heads, page_tokens, v_head_dim]
     page_tokens: int = 0
     ring_tokens: int = 0              # 0: position p sits at element p; else at p % ring_tokens
     writable: bool = True             # False: this call reads an entry that another call writes
@@ -100,9 +101,9 @@ class SequenceCache:
         self.dummy_slot = self.num_slots
         if allocate:
             for group in self.groups:
-                shape = (len(group.owners), total_pages + 1, group.request.kv_heads, page_tokens, group.request.head_dim)
-                group.k = torch.zeros(shape, dtype=dtype, device=device)
-                group.v = torch.zeros(shape, dtype=dtype, device=device)
+                shape = (len(group.owners), total_pages + 1, group.request.kv_heads, page_tokens)
+                group.k = torch.zeros((*shape, group.request.head_dim), dtype=dtype, device=device)
+                group.v = torch.zeros((*shape, group.request.v_head_dim or group.request.head_dim), dtype=dtype, device=device)
             for key, request in self._state_requests.items():
                 self._state_of[key] = torch.zeros((self.num_slots + 1, *request.shape), dtype=request.dtype, device=device)
 
@@ -145,7 +146,7 @@ class SequenceCache:
         total = 0
         for group in self.groups:
             if group.k is not None:
-                total += 2 * group.k.numel() * group.k.element_size()
+                total += (group.k.numel() + group.v.numel()) * group.k.element_size()
         for state in self._state_of.values():
             total += state.numel() * state.element_size()
         return total
@@ -153,4 +154,5 @@ class SequenceCache:
     def token_bytes(self) -> int:
         """Bytes of keys and values one cached token occupies over all full-attention entries."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.owners) * g.request.kv_heads * g.request.head_dim * size for g in self.groups)
+        return sum(len(g.owners) * g.request.kv_heads * (g.request.head_dim + (g.request.v_head_dim or g.request.head_dim)) * size
+                   for g in self.groups)

@@ -1,5 +1,6 @@
 from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .qwen3 import ConfigError, Qwen3Config
+from .lederax import LederaxConfig
 from .registry import (
     config_from_dict,
     load_config,
@@ -11,9 +12,10 @@ from .registry import (
 )
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config, model_type="qwen3")
+register_architecture("Lederax", LederaxConfig)
 
 __all__ = [
-    "ConfigError", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec", "Qwen3Config",
+    "ConfigError", "LayerCall", "LayerSpec", "LederaxConfig", "ModelSpec", "PartSpec", "Qwen3Config",
     "config_from_dict", "load_config", "load_config_dict", "load_preset", "preset_names",
     "register_architecture", "registered_architectures",
 ]

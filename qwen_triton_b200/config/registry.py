@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class.
 
-``config.json`` names its model class under ``architectures``; that name (or,
-failing that, ``model_type``) selects the typed configuration, whose
+``config.json`` names its model class under ``architectures`` (or, as a single name, under
+``architecture``); that name (or, failing that, ``model_type``) selects the typed configuration, whose
 ``model_spec()`` describes the model in parts.  The reference has no registry:
 one class switches on the family string (qwen_triton/models/core.py:108-116).
 """
@@ -49,6 +49,8 @@ def load_config_dict(model_path: str | Path) -> dict[str, Any]:
 def config_from_dict(raw: Mapping[str, Any]):
     """Pick the configuration class by ``architectures[0]``, else ``model_type``."""
     names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):
+        names.append(raw["architecture"])
     for name in names:
         if name in _BY_ARCHITECTURE:
             return _BY_ARCHITECTURE[name].from_hf_config(raw)

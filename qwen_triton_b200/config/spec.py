@@ -51,7 +51,7 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None          # None: the layer is its mixer alone
     norm: PartSpec
     extra: Mapping[str, PartSpec] = field(default_factory=dict)
 

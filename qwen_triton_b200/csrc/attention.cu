@@ -3,7 +3,9 @@
 // split-KV kernel with a combine pass for one token per sequence (decode).  Scores, softmax
 // and the weighted sum are float.  Grouped-query attention: query head h reads kv head
 // h / (nq / nkv).  Key j is visible to the query at absolute position p iff j <= p and, for a
-// windowed group, j > p - window.
+// windowed group, j > p - window.  Values may have a head size `dv` of their own.  With `r1`/`r2`
+// (one float per query head each) a score loses r1_h * ln(1 + r2_h * (p - j)): a penalty that grows
+// with the logarithm of the distance, computed in float like the score itself.
 //
 // Counterparts in luozoupi/Qwen-Triton: kernels/flash_attention.py:54-152 (one kernel for both
 // cases, no split, no window) and the masked SDPA branch of modules/attention.py:110-123 with
@@ -17,14 +19,19 @@ using namespace qt;
 struct AttnParams {
     const void* q;        // [T, nq, d]
     const void* k_cache;  // [pages, nkv, page_tokens, d]
-    const void* v_cache;
-    void* out;            // [T, nq, d]
+    const void* v_cache;  // [pages, nkv, page_tokens, dv]
+    void* out;            // [T, nq, dv]
     const int* block_table; int max_blocks;
     const int* seq_start;  // [B + 1] first token row of each sequence in this step
     const int* seq_past;   // [B] tokens already in the cache before this step
     int n_seqs, nq, nkv, d, page_tokens, ring_tokens, window;   // window <= 0: all keys
     float scale;
+    int dv;               // head size of the values
+    const float* r1;      // [nq] distance penalty r1 * ln(1 + r2 * distance), or null for none
+    const float* r2;
 };
+
+__device__ __forceinline__ float distance_penalty(float r1, float r2, int distance) { return r1 * logf(1.f + r2 * (float)distance); }
 
 // ----------------------------------------------------------------------------- many tokens per sequence
 constexpr int PF_BQ = 16;       // queries per block
@@ -37,12 +44,12 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float smem[];
-    const int d = p.d;
+    const int d = p.d, dv = p.dv;
     const int kstride = d + 1;
     float* qs = smem;                         // [PF_BQ][d]
     float* ks = qs + PF_BQ * d;               // [PF_BK][d + 1]
-    float* vs = ks + PF_BK * kstride;         // [PF_BK][d]
-    float* ps = vs + PF_BK * d;               // [PF_BQ][PF_BK]
+    float* vs = ks + PF_BK * kstride;         // [PF_BK][dv]
+    float* ps = vs + PF_BK * dv;              // [PF_BQ][PF_BK]
 
     const int seq = blockIdx.z, head = blockIdx.y;
     const int q_begin = p.seq_start[seq], q_len = p.seq_start[seq + 1] - q_begin;
@@ -56,6 +63,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
     const T* q = (const T*)p.q;
     const T* kc = (const T*)p.k_cache;
     const T* vc = (const T*)p.v_cache;
+    const bool penalised = p.r1 != nullptr;
+    const float r1 = penalised ? p.r1[head] : 0.f, r2 = penalised ? p.r2[head] : 0.f;
 
     for (int r = warp; r < PF_BQ; r += PF_WARPS)
         for (int c = lane; c < d; c += 32)
@@ -77,12 +86,12 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
             const int key = k0 + r;
             if (key <= p_last) {
                 const size_t off = cache_offset(table, key, p.ring_tokens, p.page_tokens, p.nkv, kvh, d);
-                for (int c = lane; c < d; c += 32) {
-                    ks[r * kstride + c] = to_float(kc[off + c]);
-                    vs[r * d + c] = to_float(vc[off + c]);
-                }
+                const size_t voff = cache_offset(table, key, p.ring_tokens, p.page_tokens, p.nkv, kvh, dv);
+                for (int c = lane; c < d; c += 32) ks[r * kstride + c] = to_float(kc[off + c]);
+                for (int c = lane; c < dv; c += 32) vs[r * dv + c] = to_float(vc[voff + c]);
             } else {
-                for (int c = lane; c < d; c += 32) { ks[r * kstride + c] = 0.f; vs[r * d + c] = 0.f; }
+                for (int c = lane; c < d; c += 32) ks[r * kstride + c] = 0.f;
+                for (int c = lane; c < dv; c += 32) vs[r * dv + c] = 0.f;
             }
         }
         __syncthreads();
@@ -94,6 +103,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
             float s = 0.f;
             for (int c = 0; c < d; ++c) s += qs[r * d + c] * ks[lane * kstride + c];
             const bool visible = r < rows && key <= pos && (p.window <= 0 || key > pos - p.window);
+            if (penalised && visible) s -= distance_penalty(r1, r2, pos - key);
             s = visible ? s : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(s));
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
@@ -114,7 +124,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
 #pragma unroll
                 for (int j = 0; j < DMAX / 32; ++j) {
                     const int c = lane + 32 * j;
-                    if (c < d) acc[i][j] += w * vs[kk * d + c];
+                    if (c < dv) acc[i][j] += w * vs[kk * dv + c];
                 }
             }
         }
@@ -128,14 +138,14 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
 #pragma unroll
         for (int j = 0; j < DMAX / 32; ++j) {
             const int c = lane + 32 * j;
-            if (c < d) out[((size_t)(q_begin + q0 + r) * p.nq + head) * d + c] = from_float<T>(acc[i][j] * inv);
+            if (c < dv) out[((size_t)(q_begin + q0 + r) * p.nq + head) * dv + c] = from_float<T>(acc[i][j] * inv);
         }
     }
 }
 
 template <typename T, int DMAX>
 static int launch_prefill(const AttnParams& p, int max_q_len, cudaStream_t stream) {
-    const size_t smem = ((size_t)PF_BQ * p.d + (size_t)PF_BK * (p.d + 1) + (size_t)PF_BK * p.d + PF_BQ * PF_BK) * sizeof(float);
+    const size_t smem = ((size_t)PF_BQ * p.d + (size_t)PF_BK * (p.d + 1) + (size_t)PF_BK * p.dv + PF_BQ * PF_BK) * sizeof(float);
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_prefill_kernel<T, DMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
@@ -148,9 +158,12 @@ static int launch_prefill(const AttnParams& p, int max_q_len, cudaStream_t strea
     return QT_OK;
 }
 
-static int check_common(const char* name, int n_seqs, int nq, int nkv, int d, int page_tokens, int ring_tokens, int window) {
+static int check_common(const char* name, int n_seqs, int nq, int nkv, int d, int dv, const float* r1, const float* r2, int page_tokens,
+                        int ring_tokens, int window) {
     QT_REQUIRE(n_seqs > 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "%s: bad head counts nq=%d nkv=%d (B=%d)", name, nq, nkv, n_seqs);
     QT_REQUIRE(d > 0 && d <= 256, "%s: head_dim=%d is outside 1..256", name, d);
+    QT_REQUIRE(dv > 0 && dv <= 256, "%s: value head_dim=%d is outside 1..256", name, dv);
+    QT_REQUIRE((r1 == nullptr) == (r2 == nullptr), "%s: the distance penalty needs both of its factors", name);
     QT_REQUIRE(page_tokens > 0 && ring_tokens >= 0, "%s: bad cache geometry", name);
     QT_REQUIRE(ring_tokens == 0 || (window > 0 && ring_tokens >= window), "%s: a ring of %d tokens cannot hold a window of %d", name, ring_tokens, window);
     return QT_OK;
@@ -159,16 +172,17 @@ static int check_common(const char* name, int n_seqs, int nq, int nkv, int d, in
 extern "C" int qt_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                     const int* block_table, int max_blocks, const int* seq_start, const int* seq_past,
                                     int n_seqs, int max_q_len, int nq, int nkv, int d, int page_tokens, int ring_tokens,
-                                    int window, float scale, void* stream) {
+                                    int window, float scale, int dv, const float* r1, const float* r2, void* stream) {
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
-    int rc = check_common("attention_prefill", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
+    int rc = check_common("attention_prefill", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window);
     if (rc) return rc;
     QT_REQUIRE(nq <= 65535 && n_seqs <= 65535, "attention_prefill: too many heads or sequences for one launch");
-    AttnParams p{q, k_cache, v_cache, out, block_table, max_blocks, seq_start, seq_past, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale};
+    AttnParams p{q, k_cache, v_cache, out, block_table, max_blocks, seq_start, seq_past, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale,
+                 dv, r1, r2};
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "attention_prefill", {
-        if (d <= 64) return launch_prefill<T, 64>(p, max_q_len, s);
-        if (d <= 128) return launch_prefill<T, 128>(p, max_q_len, s);
+        if (dv <= 64) return launch_prefill<T, 64>(p, max_q_len, s);
+        if (dv <= 128) return launch_prefill<T, 128>(p, max_q_len, s);
         return launch_prefill<T, 256>(p, max_q_len, s);
     });
 }
@@ -185,7 +199,7 @@ struct DecodeParams {
     AttnParams a;
     const int* seq_len;   // [B] keys visible to the token of this step (its own included)
     int n_splits;
-    float* part_acc;      // [B, nq, n_splits, d]
+    float* part_acc;      // [B, nq, n_splits, dv]
     float* part_ml;       // [B, nq, n_splits, 2]
 };
 
@@ -195,7 +209,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     pdl_wait();
     const AttnParams& p = dp.a;
     extern __shared__ float smem[];
-    const int d = p.d;
+    const int d = p.d, dv = p.dv;
     const int group = p.nq / p.nkv;
     const int chunks_per_kv = (group + DEC_HEADS - 1) / DEC_HEADS;
     const int kvh = blockIdx.y / chunks_per_kv;
@@ -204,8 +218,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     const int seq = blockIdx.z, split = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* qs = smem;                                   // [DEC_HEADS][d], scaled
-    float* red_acc = qs + DEC_HEADS * d;                // [DEC_WARPS][DEC_HEADS][d]
-    float* red_ml = red_acc + DEC_WARPS * DEC_HEADS * d; // [DEC_WARPS][DEC_HEADS][2]
+    float* red_acc = qs + DEC_HEADS * d;                // [DEC_WARPS][DEC_HEADS][dv]
+    float* red_ml = red_acc + DEC_WARPS * DEC_HEADS * dv; // [DEC_WARPS][DEC_HEADS][2]
 
     const int len = dp.seq_len[seq];
     const int lo = p.window > 0 ? max(0, len - p.window) : 0;
@@ -218,6 +232,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     const T* kc = (const T*)p.k_cache;
     const T* vc = (const T*)p.v_cache;
     const int head_base = kvh * group + h0;
+    const bool penalised = p.r1 != nullptr;
+    float r1[DEC_HEADS], r2[DEC_HEADS];
+#pragma unroll
+    for (int h = 0; h < DEC_HEADS; ++h) {
+        r1[h] = penalised && h < nh ? p.r1[head_base + h] : 0.f;
+        r2[h] = penalised && h < nh ? p.r2[head_base + h] : 0.f;
+    }
 
     for (int i = threadIdx.x; i < DEC_HEADS * d; i += blockDim.x) {
         const int h = i / d, c = i % d;
@@ -246,6 +267,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
 #pragma unroll
                 for (int h = 0; h < DEC_HEADS; ++h) s[h] += qs[h * d + c] * kv;
             }
+            if (penalised) {
+#pragma unroll
+                for (int h = 0; h < DEC_HEADS; ++h) s[h] -= distance_penalty(r1[h], r2[h], len - 1 - key);
+            }
         }
         float e[DEC_HEADS];
 #pragma unroll
@@ -261,12 +286,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
         }
         const int n_keys = min(32, k_end - k0);
         for (int kk = 0; kk < n_keys; ++kk) {
-            const T* vrow = vc + cache_offset(table, k0 + kk, p.ring_tokens, p.page_tokens, p.nkv, kvh, d);
+            const T* vrow = vc + cache_offset(table, k0 + kk, p.ring_tokens, p.page_tokens, p.nkv, kvh, dv);
             float v[DMAX / 32];
 #pragma unroll
             for (int j = 0; j < DMAX / 32; ++j) {
                 const int c = lane + 32 * j;
-                v[j] = c < d ? to_float(vrow[c]) : 0.f;
+                v[j] = c < dv ? to_float(vrow[c]) : 0.f;
             }
 #pragma unroll
             for (int h = 0; h < DEC_HEADS; ++h) {
@@ -284,12 +309,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
 #pragma unroll
         for (int j = 0; j < DMAX / 32; ++j) {
             const int c = lane + 32 * j;
-            if (c < d) red_acc[(warp * DEC_HEADS + h) * d + c] = acc[h][j];
+            if (c < dv) red_acc[(warp * DEC_HEADS + h) * dv + c] = acc[h][j];
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < nh * d; i += blockDim.x) {
-        const int h = i / d, c = i % d;
+    for (int i = threadIdx.x; i < nh * dv; i += blockDim.x) {
+        const int h = i / dv, c = i % dv;
         float m_all = -INFINITY;
         for (int w = 0; w < DEC_WARPS; ++w) m_all = fmaxf(m_all, red_ml[(w * DEC_HEADS + h) * 2]);
         float l_all = 0.f, a_all = 0.f;
@@ -297,14 +322,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
             const float mw = red_ml[(w * DEC_HEADS + h) * 2];
             const float f = mw == -INFINITY ? 0.f : expf(mw - m_all);
             l_all += red_ml[(w * DEC_HEADS + h) * 2 + 1] * f;
-            a_all += red_acc[(w * DEC_HEADS + h) * d + c] * f;
+            a_all += red_acc[(w * DEC_HEADS + h) * dv + c] * f;
         }
         const int head = head_base + h;
         if (dp.n_splits == 1) {
-            ((T*)p.out)[((size_t)seq * p.nq + head) * d + c] = from_float<T>(a_all / l_all);
+            ((T*)p.out)[((size_t)seq * p.nq + head) * dv + c] = from_float<T>(a_all / l_all);
         } else {
             const size_t slot = ((size_t)seq * p.nq + head) * dp.n_splits + split;
-            dp.part_acc[slot * d + c] = a_all;
+            dp.part_acc[slot * dv + c] = a_all;
             if (c == 0) { dp.part_ml[slot * 2] = m_all; dp.part_ml[slot * 2 + 1] = l_all; }
         }
     }
@@ -337,7 +362,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc, con
 template <typename T, int DMAX, int DEC_HEADS>
 static int launch_decode_heads(const DecodeParams& dp, cudaStream_t stream) {
     const AttnParams& p = dp.a;
-    const size_t smem = ((size_t)DEC_HEADS * p.d + (size_t)DEC_WARPS * DEC_HEADS * p.d + DEC_WARPS * DEC_HEADS * 2) * sizeof(float);
+    const size_t smem = ((size_t)DEC_HEADS * p.d + (size_t)DEC_WARPS * DEC_HEADS * p.dv + DEC_WARPS * DEC_HEADS * 2) * sizeof(float);
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel<T, DMAX, DEC_HEADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
@@ -349,7 +374,7 @@ static int launch_decode_heads(const DecodeParams& dp, cudaStream_t stream) {
     launch_kernel(attention_decode_kernel<T, DMAX, DEC_HEADS>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, dp);
     QT_CHECK_LAUNCH("attention_decode");
     if (dp.n_splits > 1) {
-        launch_kernel(attention_combine_kernel<T>, dim3(p.n_seqs * p.nq), dim3(128), 0, stream, dp.part_acc, dp.part_ml, (T*)p.out, dp.n_splits, p.d);
+        launch_kernel(attention_combine_kernel<T>, dim3(p.n_seqs * p.nq), dim3(128), 0, stream, dp.part_acc, dp.part_ml, (T*)p.out, dp.n_splits, p.dv);
         QT_CHECK_LAUNCH("attention_combine");
     }
     return QT_OK;
@@ -364,24 +389,26 @@ static int launch_decode(const DecodeParams& dp, cudaStream_t stream) {
     return launch_decode_heads<T, DMAX, 8>(dp, stream);
 }
 
-// Scratch the caller provides for n_splits > 1: part_acc of B * nq * n_splits * d floats and
+// Scratch the caller provides for n_splits > 1: part_acc of B * nq * n_splits * dv floats and
 // part_ml of B * nq * n_splits * 2 floats.
 extern "C" int qt_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                    const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
                                    int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
-                                   int n_splits, float* part_acc, float* part_ml, void* stream) {
+                                   int n_splits, float* part_acc, float* part_ml, int dv, const float* r1, const float* r2,
+                                   void* stream) {
     if (n_seqs == 0) return QT_OK;
-    int rc = check_common("attention_decode", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
+    int rc = check_common("attention_decode", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window);
     if (rc) return rc;
     QT_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: n_splits=%d", n_splits);
     QT_REQUIRE(n_splits == 1 || (part_acc && part_ml), "attention_decode: split results need scratch memory");
     QT_REQUIRE(n_seqs <= 65535, "attention_decode: too many sequences for one launch");
-    DecodeParams dp{{q, k_cache, v_cache, out, block_table, max_blocks, nullptr, nullptr, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale},
+    DecodeParams dp{{q, k_cache, v_cache, out, block_table, max_blocks, nullptr, nullptr, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale,
+                     dv, r1, r2},
                     seq_len, n_splits, part_acc, part_ml};
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "attention_decode", {
-        if (d <= 64) return launch_decode<T, 64>(dp, s);
-        if (d <= 128) return launch_decode<T, 128>(dp, s);
+        if (dv <= 64) return launch_decode<T, 64>(dp, s);
+        if (dv <= 128) return launch_decode<T, 128>(dp, s);
         return launch_decode<T, 256>(dp, s);
     });
 }

@@ -10,10 +10,10 @@
 using namespace qt;
 
 // ----------------------------------------------------------------------------- embedding
-// residual[t, :] = table[ids[t], :] widened to float.  One block per token.
+// residual[t, :] = table[ids[t], :] widened to float, times `scale` (1 for a plain gather).  One block per token.
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ residual, const T* __restrict__ table,
-                                 const int* __restrict__ ids, int hidden, int vocab) {
+                                 const int* __restrict__ ids, int hidden, int vocab, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -21,15 +21,15 @@ __global__ void embedding_kernel(float* __restrict__ residual, const T* __restri
     const bool valid = id >= 0 && id < vocab;   // ids are range-checked on the host; never read outside the table
     const T* row = table + (size_t)(valid ? id : 0) * hidden;
     float* out = residual + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = valid ? to_float(row[i]) : 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = valid ? to_float(row[i]) * scale : 0.f;
 }
 
 extern "C" int qt_embedding(float* residual, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
-                            int table_dtype, void* stream) {
+                            int table_dtype, float scale, void* stream) {
     QT_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d", n_tokens, hidden, vocab);
     if (n_tokens == 0) return QT_OK;
     return QT_DISPATCH_DTYPE(table_dtype, "embedding", {
-        launch_kernel(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, residual, (const T*)table, ids, hidden, vocab);
+        launch_kernel(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, residual, (const T*)table, ids, hidden, vocab, scale);
         QT_CHECK_LAUNCH("embedding");
         return QT_OK;
     });
@@ -63,30 +63,36 @@ extern "C" int qt_add_bias(float* out, const float* bias, int rows, int cols, vo
 //   out[r] = x * rsqrt(mean(x^2) + eps) * weight       (rounded once to the output type)
 // With `rows` the kernel norms only the listed rows (the positions whose logits are wanted) and
 // leaves the stream untouched.
+// Norm in groups: a row of `width` elements is `gridDim.y` equal consecutive parts of `hidden` elements, each
+// divided by its own root mean square (blockIdx.y is the part); one part is the plain norm.
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
                                    size_t split_stride, const float* __restrict__ weight, float eps,
-                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden, int width) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
-    float* res = residual + (size_t)src * hidden;
+    const size_t part = (size_t)blockIdx.y * hidden;
+    float* res = residual + (size_t)src * width + part;
+    if (delta) delta += part;
+    weight += part;
+    out += part;
     float sq = 0.f;
     // pass 1: form the new stream value; keep it in `res` (or, for listed rows, recompute in pass 2)
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float x = res[i];
-        if (delta) x += load_sum(delta, (size_t)src * hidden + i, n_splits, split_stride);
+        if (delta) x += load_sum(delta, (size_t)src * width + i, n_splits, split_stride);
         if (!rows) res[i] = x;
         sq += x * x;
     }
     const float total = block_sum(sq, scratch);
     const float inv = rsqrtf(total / (float)hidden + eps);
-    TO* o = out + (size_t)r * hidden;
+    TO* o = out + (size_t)r * width;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float x = res[i];   // each thread re-reads what it wrote itself
-        if (rows && delta) x += load_sum(delta, (size_t)src * hidden + i, n_splits, split_stride);
+        if (rows && delta) x += load_sum(delta, (size_t)src * width + i, n_splits, split_stride);
         o[i] = from_float<TO>(x * inv * weight[i]);
     }
 }
@@ -130,13 +136,17 @@ __device__ __forceinline__ void add_splits4(float4& v, const TD* dp, int first, 
 template <typename TD, typename TO, int BATCH, int MAX_THREADS, int MIN_BLOCKS>
 __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
                                        size_t split_stride, const float* __restrict__ weight, float eps,
-                                       TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+                                       TO* __restrict__ out, const int* __restrict__ rows, int hidden, int width) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
-    float* res = residual + (size_t)src * hidden;
+    const size_t part = (size_t)blockIdx.y * hidden;          // norm in groups: see add_rmsnorm_kernel
+    float* res = residual + (size_t)src * width + part;
+    if (delta) delta += part;
+    weight += part;
+    out += part;
     const int chunks = hidden >> 2;
     float4 x[NORM_CACHE];
     float sq = 0.f;
@@ -145,7 +155,7 @@ __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) add_rmsnorm_vec_kerne
         const int c = threadIdx.x + i * blockDim.x;
         if (c < chunks) {
             float4 v = load4(res + 4 * c);
-            if (delta) add_splits4<BATCH>(v, delta + (size_t)src * hidden + 4 * c, 0, n_splits, split_stride);
+            if (delta) add_splits4<BATCH>(v, delta + (size_t)src * width + 4 * c, 0, n_splits, split_stride);
             if (!rows) store4(res + 4 * c, v);
             x[i] = v;
             sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -153,7 +163,7 @@ __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) add_rmsnorm_vec_kerne
     }
     const float total = block_sum(sq, scratch);
     const float inv = rsqrtf(total / (float)hidden + eps);
-    TO* o = out + (size_t)r * hidden;
+    TO* o = out + (size_t)r * width;
 #pragma unroll
     for (int i = 0; i < NORM_CACHE; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
@@ -206,15 +216,17 @@ __global__ void __launch_bounds__(1024, 1) add_rmsnorm_cluster_kernel(float* __r
 
 extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int n_splits, long long split_stride,
                               const float* weight, float eps, void* out, int out_dtype, const int* rows, int n_rows,
-                              int hidden, void* stream) {
-    QT_REQUIRE(n_rows >= 0 && hidden > 0 && n_splits >= 1, "add_rmsnorm: bad sizes rows=%d H=%d splits=%d", n_rows, hidden, n_splits);
+                              int width, int groups, void* stream) {
+    QT_REQUIRE(n_rows >= 0 && width > 0 && n_splits >= 1, "add_rmsnorm: bad sizes rows=%d H=%d splits=%d", n_rows, width, n_splits);
+    QT_REQUIRE(groups >= 1 && groups <= 65535 && width % groups == 0, "add_rmsnorm: %d groups do not divide a width of %d", groups, width);
     QT_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
     if (n_rows == 0) return QT_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    const int hidden = width / groups;          // elements that share a root mean square
     // the vector kernel needs 16-byte aligned rows everywhere and at most NORM_CACHE chunks per thread
     const bool aligned = hidden % 4 == 0 && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
                          ((uintptr_t)weight % 16 == 0) && (!delta || ((uintptr_t)delta % 16 == 0 && split_stride % 4 == 0));
-    if (aligned && n_rows < 256 && hidden >= 4 * 32 * NORM_CLUSTER && hidden <= 4 * 1024 * NORM_CLUSTER) {
+    if (aligned && groups == 1 && n_rows < 256 && hidden >= 4 * 32 * NORM_CLUSTER && hidden <= 4 * 1024 * NORM_CLUSTER) {
         const int per_block = (hidden / 4 + NORM_CLUSTER - 1) / NORM_CLUSTER;
         const int cthreads = ((per_block + 31) / 32) * 32;
 #define QT_LAUNCH_NORM_CLUSTER(TD, TO)                                                                                  \
@@ -238,14 +250,14 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
         if (vthreads < 64) vthreads = 64;
         // many rows in blocks of up to 256 threads: few registers, five blocks per SM (partial sums of a split product
         // are rare there); otherwise up to 1,024 threads with eight loads of partial sums in flight
-#define QT_NORM_VEC_ARGS residual, (const TD_*)delta, n_splits, (size_t)split_stride, weight, eps, (TO_*)out, rows, hidden
+#define QT_NORM_VEC_ARGS residual, (const TD_*)delta, n_splits, (size_t)split_stride, weight, eps, (TO_*)out, rows, hidden, width
 #define QT_LAUNCH_NORM_VEC(TD, TO)                                                                                      \
     do {                                                                                                                \
         using TD_ = TD; using TO_ = TO;                                                                                 \
         if (per_thread > 1 && vthreads <= 256)                                                                          \
-            launch_kernel(add_rmsnorm_vec_kernel<TD, TO, 2, 256, 5>, dim3(n_rows), dim3(vthreads), 0, s, QT_NORM_VEC_ARGS); \
+            launch_kernel(add_rmsnorm_vec_kernel<TD, TO, 2, 256, 5>, dim3(n_rows, groups), dim3(vthreads), 0, s, QT_NORM_VEC_ARGS); \
         else                                                                                                            \
-            launch_kernel(add_rmsnorm_vec_kernel<TD, TO, 8, 1024, 1>, dim3(n_rows), dim3(vthreads), 0, s, QT_NORM_VEC_ARGS); \
+            launch_kernel(add_rmsnorm_vec_kernel<TD, TO, 8, 1024, 1>, dim3(n_rows, groups), dim3(vthreads), 0, s, QT_NORM_VEC_ARGS); \
     } while (0)
         if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_NORM_VEC(float, float);
         else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_NORM_VEC(float, __nv_bfloat16);
@@ -259,8 +271,8 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     }
     const int threads = hidden >= 2048 ? 512 : 256;
 #define QT_LAUNCH_NORM(TD, TO)                                                                                   \
-    launch_kernel(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, s, residual, (const TD*)delta, n_splits, (size_t)split_stride, \
-                                                          weight, eps, (TO*)out, rows, hidden)
+    launch_kernel(add_rmsnorm_kernel<TD, TO>, dim3(n_rows, groups), dim3(threads), 0, s, residual, (const TD*)delta, n_splits, (size_t)split_stride, \
+                                                          weight, eps, (TO*)out, rows, hidden, width)
     if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_NORM(float, float);
     else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_NORM(float, __nv_bfloat16);
     else if (delta_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_NORM(__nv_bfloat16, __nv_bfloat16);
@@ -562,6 +574,105 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     else QT_FAIL(QT_ERR_ARG, "qk_norm_rope_write: unsupported element types %d -> %d", in_dtype, out_dtype);
 #undef QT_LAUNCH_QKV
     QT_CHECK_LAUNCH("qk_norm_rope_write");
+    return QT_OK;
+}
+
+// ----------------------------------------------------------------------------- projection bias + value norm + value blend + cache write
+// For mixers without rotation whose values are treated before they are cached.  Input: the fused projection output
+// [t, nq * d + nkv * d + nkv * dv] (possibly split-K partial sums), the value head size dv free of the q/k size d.
+// One warp per (token, head), everything in float:
+//   q head:  + bias, store to q_out[t, h, :]
+//   k head:  + bias, store into the key cache at the token's position
+//   v head:  + bias; with v_norm divided by sqrt(mean(v^2) + v_eps); with blend_from,
+//            v = (1 - lambda) v + lambda * blend_from[t, kv head, :], lambda read from the device;
+//            with keep_to, keep_to[t, kv head, :] = v (float: what a later layer blends with);
+//            store into the value cache.
+struct QkvTreatParams {
+    const void* qkv; int n_splits; size_t split_stride;
+    const float* bias;                    // [nq * d + nkv * d + nkv * dv] or null
+    void* q_out; void* k_cache; void* v_cache;
+    const int* token_seq; const int* token_pos; const int* block_table; int max_blocks;
+    int v_norm; float v_eps;
+    const float* blend_from; const float* blend_lambda; float* keep_to;
+    int n_tokens, nq, nkv, d, dv, page_tokens, ring_tokens, write_kv;
+};
+
+template <typename TI, typename TO>
+__global__ void qkv_treat_write_kernel(const QkvTreatParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = p.nq + 2 * p.nkv;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long long)p.n_tokens * heads_total) return;
+    const int t = (int)(item / heads_total);
+    const int head = (int)(item % heads_total);
+    const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
+    if (!is_q && !p.write_kv) return;
+    const int row_width = (p.nq + p.nkv) * p.d + p.nkv * p.dv;
+    const int col0 = is_q ? head * p.d : (is_k ? p.nq * p.d + (head - p.nq) * p.d : (p.nq + p.nkv) * p.d + (head - p.nq - p.nkv) * p.dv);
+    const int len = (is_q || is_k) ? p.d : p.dv;
+    const TI* in = (const TI*)p.qkv + (size_t)t * row_width + col0;
+    const float* bias = p.bias ? p.bias + col0 : nullptr;
+    const int pos = p.token_pos[t];
+    if (is_q || is_k) {
+        TO* dst;
+        if (is_q) dst = (TO*)p.q_out + ((size_t)t * p.nq + head) * p.d;
+        else {
+            const int* table = p.block_table + (size_t)p.token_seq[t] * p.max_blocks;
+            dst = (TO*)p.k_cache + cache_offset(table, pos, p.ring_tokens, p.page_tokens, p.nkv, head - p.nq, p.d);
+        }
+        for (int i = lane; i < len; i += 32) {
+            float x = load_sum(in, (size_t)i, p.n_splits, p.split_stride);
+            if (bias) x += bias[i];
+            dst[i] = from_float<TO>(x);
+        }
+        return;
+    }
+    const int kvh = head - p.nq - p.nkv;
+    float sq = 0.f;
+    for (int i = lane; i < len; i += 32) {
+        float x = load_sum(in, (size_t)i, p.n_splits, p.split_stride);
+        if (bias) x += bias[i];
+        sq += x * x;
+    }
+    const float inv = p.v_norm ? 1.f / sqrtf(warp_sum(sq) / (float)len + p.v_eps) : 1.f;
+    const float lambda = p.blend_from ? p.blend_lambda[0] : 0.f;
+    const size_t side = ((size_t)t * p.nkv + kvh) * p.dv;
+    const int* table = p.block_table + (size_t)p.token_seq[t] * p.max_blocks;
+    TO* dst = (TO*)p.v_cache + cache_offset(table, pos, p.ring_tokens, p.page_tokens, p.nkv, kvh, p.dv);
+    for (int i = lane; i < len; i += 32) {
+        float x = load_sum(in, (size_t)i, p.n_splits, p.split_stride);       // read again: the row is in L1 or L2
+        if (bias) x += bias[i];
+        x *= inv;
+        if (p.blend_from) x = (1.f - lambda) * x + lambda * p.blend_from[side + i];
+        if (p.keep_to) p.keep_to[side + i] = x;
+        dst[i] = from_float<TO>(x);
+    }
+}
+
+extern "C" int qt_qkv_treat_write(const void* qkv, int in_dtype, int n_splits, long long split_stride, const float* bias,
+                                  void* q_out, void* k_cache, void* v_cache, int out_dtype, const int* token_seq,
+                                  const int* token_pos, const int* block_table, int max_blocks, int v_norm, float v_eps,
+                                  const float* blend_from, const float* blend_lambda, float* keep_to, int n_tokens, int nq,
+                                  int nkv, int d, int dv, int page_tokens, int ring_tokens, int write_kv, void* stream) {
+    QT_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && dv > 0, "qkv_treat_write: bad sizes T=%d nq=%d nkv=%d d=%d dv=%d", n_tokens, nq, nkv, d, dv);
+    QT_REQUIRE(page_tokens > 0 && n_splits >= 1 && ring_tokens >= 0, "qkv_treat_write: bad cache geometry");
+    QT_REQUIRE(!write_kv || (k_cache && v_cache && block_table), "qkv_treat_write: cache pointers missing");
+    QT_REQUIRE(!blend_from || blend_lambda, "qkv_treat_write: a blend needs its weight");
+    QT_REQUIRE(!v_norm || v_eps > 0.f, "qkv_treat_write: the value norm needs a positive eps");
+    if (n_tokens == 0) return QT_OK;
+    QkvTreatParams p{qkv, n_splits, (size_t)split_stride, bias, q_out, k_cache, v_cache, token_seq, token_pos, block_table, max_blocks,
+                     v_norm, v_eps, blend_from, blend_lambda, keep_to, n_tokens, nq, nkv, d, dv, page_tokens, ring_tokens, write_kv};
+    const int warps = 4;
+    const long long items = (long long)n_tokens * (nq + 2 * nkv);
+    const unsigned grid = (unsigned)((items + warps - 1) / warps);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (in_dtype == QT_F32 && out_dtype == QT_F32) launch_kernel(qkv_treat_write_kernel<float, float>, dim3(grid), dim3(warps * 32), 0, s, p);
+    else if (in_dtype == QT_F32 && out_dtype == QT_BF16) launch_kernel(qkv_treat_write_kernel<float, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, s, p);
+    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) launch_kernel(qkv_treat_write_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, s, p);
+    else QT_FAIL(QT_ERR_ARG, "qkv_treat_write: unsupported element types %d -> %d", in_dtype, out_dtype);
+    QT_CHECK_LAUNCH("qkv_treat_write");
     return QT_OK;
 }
 

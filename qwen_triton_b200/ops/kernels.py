@@ -22,10 +22,13 @@ _c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_floa
 
 _SIGNATURES = {
     "elementwise": {
-        "qt_embedding": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_embedding": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
         "qt_add_bias": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_add_rmsnorm": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int,
-                           _c_int, _c_ptr],
+                           _c_int, _c_int, _c_ptr],
+        "qt_qkv_treat_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
+                               _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                               _c_int, _c_int, _c_ptr],
         "qt_qk_norm_rope_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                   _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
@@ -33,9 +36,13 @@ _SIGNATURES = {
     },
     "attention": {
         "qt_attention_prefill": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
-                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
         "qt_attention_decode": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
-                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
+                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    },
+    "experts": {
+        "qt_experts_by_pair": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                               _c_int, _c_int, _c_int, _c_float, _c_ptr],
     },
     "attention_mma": {
         "qt_attention_decode_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
@@ -183,8 +190,8 @@ class GemmOut:
 
 
 # ----------------------------------------------------------------------------- elementwise
-def embedding(residual: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
-    """residual[t] = table[ids[t]] in float.  ids: int32 [T]."""
+def embedding(residual: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> None:
+    """residual[t] = table[ids[t]] * scale in float.  ids: int32 [T]."""
     tokens, hidden = residual.shape
     _need(residual, "residual", torch.float32)
     _need(table, "table")
@@ -192,7 +199,7 @@ def embedding(residual: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) ->
     if table.shape[1] != hidden:
         raise KernelError(f"embedding: table width {table.shape[1]} != stream width {hidden}")
     _call("elementwise", "qt_embedding", _ptr(residual), _ptr(table), _ptr(ids), tokens, hidden, table.shape[0],
-          _code(table, "table"), _stream())
+          _code(table, "table"), float(scale), _stream())
 
 
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
@@ -205,13 +212,16 @@ def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: GemmOut | None, weight: torch.Tensor, eps: float,
-                out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
-    """stream += delta; out = rmsnorm(stream) * weight.
+                out: torch.Tensor, rows: torch.Tensor | None = None, groups: int = 1) -> None:
+    """stream += delta; out = rmsnorm(stream) * weight.  With ``groups`` > 1 a row is that many equal consecutive
+    parts, each divided by its own root mean square; the weight spans the whole row.
 
     Without ``rows`` every row of ``residual`` [T, H] is updated in place and normed into ``out`` [T, H].
     With ``rows`` (int32 [K]) only those rows are normed into ``out`` [K, H] and the stream is left as it is.
     """
     hidden = residual.shape[1]
+    if groups < 1 or hidden % groups:
+        raise KernelError(f"add_rmsnorm: {groups} groups do not divide a width of {hidden}")
     _need(residual, "residual", torch.float32)
     _need(weight, "weight", torch.float32, (hidden,))
     n_rows = residual.shape[0] if rows is None else rows.shape[0]
@@ -224,7 +234,48 @@ def add_rmsnorm(residual: torch.Tensor, delta: GemmOut | None, weight: torch.Ten
     _call("elementwise", "qt_add_rmsnorm", _ptr(residual), _ptr(delta.tensor) if delta else None,
           _code(delta.tensor, "delta") if delta else F32, delta.n_splits if delta else 1,
           delta.split_stride if delta else 0, _ptr(weight), float(eps), _ptr(out), _code(out, "out"), _ptr(rows),
-          n_rows, hidden, _stream())
+          n_rows, hidden, int(groups), _stream())
+
+
+def qkv_treat_write(qkv: GemmOut, bias: torch.Tensor | None, q_out: torch.Tensor, k_cache: torch.Tensor | None,
+                    v_cache: torch.Tensor | None, token_seq: torch.Tensor, token_pos: torch.Tensor,
+                    block_table: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int,
+                    page_tokens: int, ring_tokens: int, v_norm_eps: float | None = None,
+                    blend_from: torch.Tensor | None = None, blend_weight: torch.Tensor | None = None,
+                    keep_to: torch.Tensor | None = None, write_kv: bool = True) -> None:
+    """What follows the fused projection of a mixer without rotation: the bias, then q to ``q_out`` and k, v into the
+    cache.  Values (head size ``v_head_dim``) are first divided by their root mean square per head (``v_norm_eps``
+    given), then blended, v = (1 - w) v + w * ``blend_from`` [T, nkv, dv] with w = ``blend_weight`` (a float on the
+    device), then copied to ``keep_to`` [T, nkv, dv] (float), each where given.  All in float.
+
+    qkv [*, T, nq d + nkv d + nkv dv]; q_out [T, nq, d]; k cache [pages, nkv, page_tokens, d], v cache [..., dv]."""
+    tokens = qkv.rows
+    width = (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_head_dim
+    if qkv.cols != width:
+        raise KernelError(f"qkv_treat_write: projection width {qkv.cols} != nq d + nkv d + nkv dv = {width}")
+    _need(q_out, "q_out", shape=(tokens, num_heads, head_dim))
+    _need(token_seq, "token_seq", torch.int32, (tokens,))
+    _need(token_pos, "token_pos", torch.int32, (tokens,))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (width,))
+    max_blocks = 0
+    if write_kv:
+        _need(block_table, "block_table", torch.int32)
+        max_blocks = block_table.shape[1]
+        for name, cache, size in (("k_cache", k_cache, head_dim), ("v_cache", v_cache, v_head_dim)):
+            _need(cache, name, q_out.dtype)
+            if tuple(cache.shape[1:]) != (num_kv_heads, page_tokens, size):
+                raise KernelError(f"{name}: shape {tuple(cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {size}]")
+    for name, side in (("blend_from", blend_from), ("keep_to", keep_to)):
+        if side is not None:
+            _need(side, name, torch.float32, (tokens, num_kv_heads, v_head_dim))
+    if blend_from is not None:
+        _need(blend_weight, "blend_weight", torch.float32)
+    _call("elementwise", "qt_qkv_treat_write", _ptr(qkv.tensor), _code(qkv.tensor, "qkv"), qkv.n_splits, qkv.split_stride,
+          _ptr(bias), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _code(q_out, "q_out"), _ptr(token_seq), _ptr(token_pos),
+          _ptr(block_table), max_blocks, 0 if v_norm_eps is None else 1, float(v_norm_eps or 0.0), _ptr(blend_from),
+          _ptr(blend_weight), _ptr(keep_to), tokens, num_heads, num_kv_heads, head_dim, v_head_dim, page_tokens, ring_tokens,
+          1 if write_kv else 0, _stream())
 
 
 def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
@@ -302,16 +353,27 @@ def swiglu(gate_up: GemmOut, out: torch.Tensor, group: int = 0, activation: str 
 
 
 # ----------------------------------------------------------------------------- attention
-def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens):
+def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty=None):
     _need(q, "q")
     tokens, num_heads, head_dim = q.shape
-    _need(out, "out", q.dtype, q.shape)
     _need(k_cache, "k_cache", q.dtype)
-    _need(v_cache, "v_cache", q.dtype, k_cache.shape)
+    _need(v_cache, "v_cache", q.dtype)
+    v_dim = v_cache.shape[-1]                       # values may have a head size of their own
+    _need(out, "out", q.dtype, (tokens, num_heads, v_dim))
     if tuple(k_cache.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
         raise KernelError(f"cache shape {tuple(k_cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {head_dim}]")
+    if tuple(v_cache.shape[:-1]) != tuple(k_cache.shape[:-1]):
+        raise KernelError(f"value cache {tuple(v_cache.shape)} does not go with key cache {tuple(k_cache.shape)}")
     _need(block_table, "block_table", torch.int32)
+    if penalty is not None:
+        for name, factor in zip(("r1", "r2"), penalty):
+            _need(factor, f"distance penalty {name}", torch.float32, (num_heads,))
     return tokens, num_heads, head_dim
+
+
+def _plain_attention(q: torch.Tensor, v_cache: torch.Tensor, penalty) -> bool:
+    """Whether the tensor-core attention kernels may take this call: values as wide as keys, no distance penalty."""
+    return penalty is None and v_cache.shape[-1] == q.shape[2]
 
 
 def attention_mma_supported(q: torch.Tensor, page_tokens: int) -> bool:
@@ -341,10 +403,16 @@ def _pick_attention(q: torch.Tensor, page_tokens: int, impl: str | None, prefill
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                       block_table: torch.Tensor, seq_start: torch.Tensor, seq_past: torch.Tensor, max_q_len: int,
                       num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float,
-                      impl: str | None = None) -> None:
+                      impl: str | None = None, penalty: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
     """Causal attention of packed sequences over the cache (which already holds this step's keys).
-    ``impl`` forces a kernel ("tc": tcgen05, "mma": mma.sync, "generic"); by default the shape decides."""
-    _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens)
+    ``impl`` forces a kernel ("tc": tcgen05, "mma": mma.sync, "generic"); by default the shape decides.
+    ``penalty`` = (r1, r2), float [heads] each: the score of key j for the query at position i loses
+    r1_h * ln(1 + r2_h * (i - j))."""
+    _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
+    if not _plain_attention(q, v_cache, penalty):
+        if impl not in (None, "generic"):
+            raise KernelError(f"attention kernel {impl!r} takes neither a distance penalty nor values of another head size")
+        impl = "generic"
     n_seqs = seq_past.shape[0]
     _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
     _need(seq_past, "seq_past", torch.int32)
@@ -364,7 +432,8 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         return
     _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
-          num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), _stream())
+          num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), v_cache.shape[-1],
+          _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, _stream())
 
 
 def _ws_merges_in_cluster(n_splits: int, warps: int, group: int, head_dim: int) -> bool:
@@ -383,7 +452,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      block_table: torch.Tensor, seq_len: torch.Tensor, num_kv_heads: int, page_tokens: int,
                      ring_tokens: int, window: int | None, scale: float, n_splits: int,
                      part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, impl: str | None = None,
-                     warps: int = 1) -> None:
+                     warps: int = 1, penalty: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
     """One query token per sequence; ``seq_len`` counts the keys it sees (its own included).
 
     With ``n_splits`` > 1 the keys of each sequence are cut into that many ranges whose partial
@@ -392,12 +461,16 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     ranges, n_splits partial results; the default where it applies) and "mma" (the four warps of a block
     share each tile); "generic" takes every element type and head size.
     """
-    n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens)
+    n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
+    if not _plain_attention(q, v_cache, penalty):
+        if impl not in (None, "generic"):
+            raise KernelError(f"attention kernel {impl!r} takes neither a distance penalty nor values of another head size")
+        impl = "generic"
     if n_splits > 1:
         _need(part_acc, "part_acc", torch.float32)
         _need(part_ml, "part_ml", torch.float32)
-        if part_acc.numel() < n_seqs * num_heads * n_splits * head_dim or part_ml.numel() < n_seqs * num_heads * n_splits * 2:
+        if part_acc.numel() < n_seqs * num_heads * n_splits * v_cache.shape[-1] or part_ml.numel() < n_seqs * num_heads * n_splits * 2:
             raise KernelError("attention_decode: scratch is too small for this batch and split count")
     if impl == "ws" and not attention_mma_supported(q, page_tokens):
         raise KernelError(f"the tensor-core attention kernels do not take {q.dtype}, head_dim={q.shape[2]}, pages of {page_tokens}")
@@ -415,7 +488,29 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _call("attention_mma", "qt_attention_decode_mma", *common, _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
     else:
         _call("attention", "qt_attention_decode", *common[:4], _code(q, "q"), *common[4:], _ptr(part_acc), _ptr(part_ml),
+              v_cache.shape[-1], _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None,
               _stream(), launches=launches)
+
+
+# ----------------------------------------------------------------------------- experts chosen by a table
+def experts_by_pair(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
+                    mid: torch.Tensor, out: torch.Tensor, activation: str, pair_weight: float) -> None:
+    """out [T, width] (float) = pair_weight * sum over the ``top`` experts e that ``table[token_ids[t]]`` names of
+    down[e] act(up[e] x[t]): one matrix-vector pass per (token, expert) pair, the form for few tokens.
+    up [E, ff, width], down [E, width, ff], mid [T * top, ff] (scratch for the activations), all of x's element type."""
+    tokens, width = x.shape
+    experts, ff = up.shape[0], up.shape[1]
+    top = table.shape[1]
+    _need(x, "x")
+    _need(token_ids, "token_ids", torch.int32, (tokens,))
+    _need(table, "table", torch.int32)
+    _need(up, "up", x.dtype, (experts, ff, width))
+    _need(down, "down", x.dtype, (experts, width, ff))
+    _need(mid, "mid", x.dtype, (tokens * top, ff))
+    _need(out, "out", torch.float32, (tokens, width))
+    _call("experts", "qt_experts_by_pair", _ptr(x), _ptr(token_ids), _ptr(table), _ptr(up), _ptr(down), _ptr(mid), _ptr(out),
+          _code(x, "x"), tokens, table.shape[0], top, experts, width, ff, activation_code(activation), float(pair_weight),
+          _stream(), launches=2)
 
 
 # ----------------------------------------------------------------------------- matrix product

@@ -4,6 +4,23 @@ a position encoding part and an optional window.
 Order as in the reference (qwen_triton/modules/attention.py:53-73,125-128): project, norm q and k
 per head over head_dim *before* rotation, rotate, write k/v to the cache, attend, project out.
 The three projections run as one product over the row-concatenated weight [q; k; v].
+
+Further parameters, each off unless given, for designs that treat scores or values differently:
+
+* ``v_head_dim``: head size of the values where it is not the keys' (the output projection then reads
+  ``num_heads * v_head_dim`` columns);
+* ``o_bias``: whether the output projection has a bias (default: what ``bias`` says for all four);
+* ``v_norm`` with ``v_norm_eps``: every value head is divided by its root mean square before it is cached;
+* ``v_blend`` = "source" | "blend" with ``v_blend_key``: a "source" layer keeps its (treated) values of the step's
+  tokens in a float buffer named by the key; a "blend" layer replaces its own by (1 - w) v + w v_source, w being
+  the float tensor named by ``names["v_blend_weight"]``; what is blended is what is cached;
+* ``distance_penalty`` = "log": the score of key j for the query at position i loses r1_h ln(1 + r2_h (i - j)),
+  with one r1 and r2 per query head (tensors ``names["r1"]``, ``names["r2"]``);
+* ``weight_suffix`` / ``bias_suffix``: what a projection's tensor names add to the projection's name
+  (default ".weight" / ".bias").
+
+Values that are treated (``v_norm``, ``v_blend``, a head size of their own) go with no rotation and no q/k norm:
+bias, treatment and the cache write are then one kernel behind the projection (``kernels.qkv_treat_write``).
 """
 from __future__ import annotations
 
@@ -38,44 +55,86 @@ class Attention:
         self.own_kv = bool(params.get("own_kv", True))
         self.qk_norm = bool(params.get("qk_norm", False))
         self.bias = bool(params.get("bias", False))        # q, k, v and o projections with a bias (attention.py:38-41)
+        self.o_bias = bool(params.get("o_bias", self.bias))
         self.eps = float(params.get("qk_norm_eps", 1e-6))
-        self.names = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+        self.names = self._names(params)
+        self.dv = int(params.get("v_head_dim") or self.d)
+        self.v_norm_eps = float(params.get("v_norm_eps", 1e-6)) if params.get("v_norm", False) else None
+        self.v_blend = params.get("v_blend")
+        if self.v_blend not in (None, "source", "blend"):
+            raise ValueError(f"{prefix}: v_blend={self.v_blend!r} is neither 'source' nor 'blend'")
+        self.penalised = self._penalised(params, prefix)
+        self.r1 = self.r2 = self.blend_weight = self.qkv_bias = None
         if self.nq % self.nkv:
             raise ValueError(f"{prefix}: {self.nq} query heads are not a multiple of {self.nkv} kv heads")
-        if self.d > 256:
-            raise ValueError(f"{prefix}: head_dim={self.d} is beyond what the attention kernels take (256)")
+        if max(self.d, self.dv) > 256:
+            raise ValueError(f"{prefix}: head_dim={max(self.d, self.dv)} is beyond what the attention kernels take (256)")
         position_spec = params["position"]
         self.position = part_class("position", position_spec)(position_spec.params, runtime)
         self.interleaved = bool(getattr(self.position, "interleaved", False))      # which elements of a head form a rotation pair
         self.cos_sin: torch.Tensor | None = None
         self.q_weight = self.k_weight = None
-        proj_rows = (self.nq + (2 * self.nkv if self.own_kv else 0)) * self.d
-        self.qkv = Linear("attn.qkv" + (".biased" if self.bias else ""), proj_rows, self.hidden, runtime, role="qkv", bias=self.bias)
-        self.o = Linear("attn.o" + (".biased" if self.bias else ""), self.hidden, self.nq * self.d, runtime, role="attn_out", bias=self.bias)
+        # values that are treated before they are cached: bias, treatment and cache write are one kernel of their own
+        self.treated = self.v_norm_eps is not None or self.v_blend is not None or self.dv != self.d
+        if self.treated and (self.qk_norm or not self.own_kv or position_spec.kind != "none"):
+            raise ValueError(f"{prefix}: treated values (v_norm, v_blend, v_head_dim) go with no rotation, no q/k norm and keys of the layer's own")
+        # the tensor-core attention kernels take neither a distance penalty nor values of another head size
+        self.plain_scores = not self.penalised and self.dv == self.d
+        proj_rows = self.nq * self.d + (self.nkv * (self.d + self.dv) if self.own_kv else 0)
+        if self.treated:
+            self.qkv = Linear("attn.qkv.sums", proj_rows, self.hidden, runtime, float_out=True)      # float sums: the bias is added behind it
+        else:
+            self.qkv = Linear("attn.qkv" + (".biased" if self.bias else ""), proj_rows, self.hidden, runtime, role="qkv", bias=self.bias)
+        self.o = Linear("attn.o" + (".biased" if self.o_bias else ""), self.hidden, self.nq * self.dv, runtime, role="attn_out", bias=self.o_bias)
         ws = runtime.workspace
         ws.declare("attn.q", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
-        ws.declare("attn.ctx", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
-        ws.declare("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.d, torch.float32)
+        ws.declare("attn.ctx", runtime.max_step_tokens * self.nq * self.dv, runtime.dtype)
+        ws.declare("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.dv, torch.float32)
         ws.declare("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2, torch.float32)
+        self.side_name = "attn.values." + str(params.get("v_blend_key", "first"))
+        if self.v_blend is not None:
+            ws.declare(self.side_name, runtime.max_step_tokens * self.nkv * self.dv, torch.float32)
         # few tokens: the projection takes rows whose norm factor is still to be applied (``ScaledRows``)
         self.takes_scaled_rows = self.qkv.fused_capable
 
     # ------------------------------------------------------------------ weights
+    @staticmethod
+    def _names(params) -> dict[str, str]:
+        n = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm", "r1", "r2", "v_blend_weight")}
+        n["w"], n["b"] = str(params.get("weight_suffix", ".weight")), str(params.get("bias_suffix", ".bias"))
+        return n
+
+    @staticmethod
+    def _penalised(params, prefix: str) -> bool:
+        kind = params.get("distance_penalty")
+        if kind not in (None, "log"):
+            raise ValueError(f"{prefix}: distance_penalty={kind!r}; the attention kernels compute 'log'")
+        return kind is not None
+
     @classmethod
     def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
         hidden, nq, nkv, d = (int(params[k]) for k in ("hidden_size", "num_heads", "num_kv_heads", "head_dim"))
-        n = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+        dv = int(params.get("v_head_dim") or d)
+        n = cls._names(params)
         own_kv = bool(params.get("own_kv", True))
-        out = {f"{prefix}.{n['q']}.weight": TensorSpec((nq * d, hidden)),
-               f"{prefix}.{n['o']}.weight": TensorSpec((hidden, nq * d))}
+        out = {f"{prefix}.{n['q']}{n['w']}": TensorSpec((nq * d, hidden)),
+               f"{prefix}.{n['o']}{n['w']}": TensorSpec((hidden, nq * dv))}
         if own_kv:
-            out[f"{prefix}.{n['k']}.weight"] = TensorSpec((nkv * d, hidden))
-            out[f"{prefix}.{n['v']}.weight"] = TensorSpec((nkv * d, hidden))
+            out[f"{prefix}.{n['k']}{n['w']}"] = TensorSpec((nkv * d, hidden))
+            out[f"{prefix}.{n['v']}{n['w']}"] = TensorSpec((nkv * dv, hidden))
         if params.get("bias", False):
             # the reference starts a bias at zero (models/core.py:269-270); random ones so that a bias that is skipped shows
-            for name in ("q", "o") + (("k", "v") if own_kv else ()):
-                rows = out[f"{prefix}.{n[name]}.weight"].shape[0]
-                out[f"{prefix}.{n[name]}.bias"] = TensorSpec((rows,), role="vector", init_std=0.1, init_mean=0.0)
+            for name in (("q",) + (("o",) if params.get("o_bias", True) else ()) + (("k", "v") if own_kv else ())):
+                rows = out[f"{prefix}.{n[name]}{n['w']}"].shape[0]
+                out[f"{prefix}.{n[name]}{n['b']}"] = TensorSpec((rows,), role="vector", init_std=0.1, init_mean=0.0)
+        if cls._penalised(params, prefix):
+            # r2 stays positive, so that 1 + r2 * distance does; the draw's tails end six deviations from the mean
+            out[f"{prefix}.{n['r1']}"] = TensorSpec((nq,), role="vector", init_std=0.3, init_mean=1.0)
+            out[f"{prefix}.{n['r2']}"] = TensorSpec((nq,), role="vector", init_std=0.04, init_mean=0.3)
+        if params.get("v_blend") is not None or params.get("v_blend_weight_stored", False):
+            # a source layer stores the weight too and never reads it; a layer outside the scheme may store it
+            out[f"{prefix}.{n['v_blend_weight']}"] = TensorSpec((), role="vector", init_std=0.08, init_mean=0.4,
+                                                                optional=params.get("v_blend") != "blend")
         if params.get("qk_norm", False):
             out[f"{prefix}.{n['q_norm']}.weight"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
             if own_kv:
@@ -84,15 +143,25 @@ class Attention:
 
     def load(self, source) -> None:
         n, p = self.names, self.prefix
-        rows = [source(f"{p}.{n['q']}.weight")]
+        rows = [source(f"{p}.{n['q']}{n['w']}")]
         if self.own_kv:
-            rows += [source(f"{p}.{n['k']}.weight"), source(f"{p}.{n['v']}.weight")]
+            rows += [source(f"{p}.{n['k']}{n['w']}"), source(f"{p}.{n['v']}{n['w']}")]
         self.qkv.set_weight(torch.cat([r.to(self.runtime.dtype) for r in rows], dim=0))
-        self.o.set_weight(source(f"{p}.{n['o']}.weight"))
+        self.o.set_weight(source(f"{p}.{n['o']}{n['w']}"))
         if self.bias:
             names = ("q", "k", "v") if self.own_kv else ("q",)
-            self.qkv.set_bias(torch.cat([source(f"{p}.{n[name]}.bias").float() for name in names], dim=0))
-            self.o.set_bias(source(f"{p}.{n['o']}.bias"))
+            bias = torch.cat([source(f"{p}.{n[name]}{n['b']}").float() for name in names], dim=0)
+            if self.treated:
+                self.qkv_bias = to_device(bias, torch.float32, self.runtime.device)
+            else:
+                self.qkv.set_bias(bias)
+            if self.o_bias:
+                self.o.set_bias(source(f"{p}.{n['o']}{n['b']}"))
+        if self.penalised:
+            self.r1 = to_device(source(f"{p}.{n['r1']}"), torch.float32, self.runtime.device)
+            self.r2 = to_device(source(f"{p}.{n['r2']}"), torch.float32, self.runtime.device)
+        if self.v_blend == "blend":
+            self.blend_weight = to_device(source(f"{p}.{n['v_blend_weight']}"), torch.float32, self.runtime.device).reshape(1)
         if self.qk_norm:
             self.q_weight = to_device(source(f"{p}.{n['q_norm']}.weight"), torch.float32, self.runtime.device)
             if self.own_kv:
@@ -105,7 +174,7 @@ class Attention:
 
     # ------------------------------------------------------------------ cache
     def cache_request(self) -> KVRequest | None:
-        return KVRequest(self.nkv, self.d, self.window)
+        return KVRequest(self.nkv, self.d, self.window, self.dv if self.dv != self.d else None)
 
     # ------------------------------------------------------------------ run
     def _splits(self, ctx, cache) -> tuple[int, int]:
@@ -121,7 +190,7 @@ class Attention:
         span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
         group = self.nq // self.nkv
         most = max(1, min(_MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
-        if self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128 and cache.page_tokens == 64:
+        if self.plain_scores and self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128 and cache.page_tokens == 64:
             pairs = ctx.n_seqs * self.nkv * math.ceil(group / 16)
             tiles = math.ceil(span / 32)
             sms = self.runtime.sm_count
@@ -172,11 +241,19 @@ class Attention:
         tokens = x.shape[0]
         ws = self.runtime.workspace
         q = ws.view("attn.q", tokens, self.nq, self.d)
-        out = ws.view("attn.ctx", tokens, self.nq, self.d)
+        out = ws.view("attn.ctx", tokens, self.nq, self.dv)
         table = ctx.block_table(cache.group)
         write = cache.writable and self.own_kv
         rotary_dim = 0 if self.cos_sin is None else self.cos_sin.shape[1]
-        if self.qkv.fusable(tokens) and kernels.fused_qkv_supported(self.d, rotary_dim):
+        penalty = (self.r1, self.r2) if self.penalised else None
+        if self.treated:
+            side = ws.view(self.side_name, tokens, self.nkv, self.dv) if self.v_blend is not None else None
+            kernels.qkv_treat_write(self.qkv(x), self.qkv_bias, q, cache.k if write else None, cache.v if write else None,
+                                    ctx.token_seq, ctx.token_pos, table if write else None, self.nq, self.nkv, self.d, self.dv,
+                                    cache.page_tokens, cache.ring_tokens, v_norm_eps=self.v_norm_eps,
+                                    blend_from=side if self.v_blend == "blend" else None, blend_weight=self.blend_weight,
+                                    keep_to=side if self.v_blend == "source" else None, write_kv=write)
+        elif self.qkv.fusable(tokens) and kernels.fused_qkv_supported(self.d, rotary_dim):
             # few tokens: per-head norm, rotation and the cache write in the projection's epilogue
             self.qkv.into_qkv(x, q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
                               table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv,
@@ -190,10 +267,10 @@ class Attention:
             n_splits, warps = self._splits(ctx, cache)
             kernels.attention_decode(q, cache.k, cache.v, out, table, ctx.seq_len, self.nkv, cache.page_tokens,
                                      cache.ring_tokens, self.window, self.scale, n_splits,
-                                     ws.view("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.d),
-                                     ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2), warps=warps)
+                                     ws.view("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.dv),
+                                     ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2), warps=warps, penalty=penalty)
         else:
             kernels.attention_prefill(q, cache.k, cache.v, out, table, ctx.seq_start, ctx.seq_past, ctx.max_q_len,
-                                      self.nkv, cache.page_tokens, cache.ring_tokens, self.window, self.scale)
-        out = out.view(tokens, self.nq * self.d)
+                                      self.nkv, cache.page_tokens, cache.ring_tokens, self.window, self.scale, penalty=penalty)
+        out = out.view(tokens, self.nq * self.dv)
         return DeferredProduct(self.o, out) if self.o.fusable(tokens) else self.o(out)

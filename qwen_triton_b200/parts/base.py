@@ -70,11 +70,13 @@ def part_class(family: str, spec: PartSpec) -> type:
 # ----------------------------------------------------------------------------- what a mixer keeps per sequence
 @dataclass(frozen=True)
 class KVRequest:
-    """Keys and values per token: all of them (``window`` None) or the last ``window``."""
+    """Keys and values per token: all of them (``window`` None) or the last ``window``.  Values have the keys' head
+    size unless ``v_head_dim`` gives their own."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
 
 
 @dataclass(frozen=True)

@@ -1,9 +1,12 @@
 """Arrangements of norm, mixer and feed-forward around the residual stream.
 
 ``pre_norm``: h += mixer(norm(h)); h += feed_forward(norm(h)) (qwen_triton/models/core.py:126-152).
-Each addition is left pending on the stream and folded in by the next norm kernel.
+Each addition is left pending on the stream and folded in by the next norm kernel.  A layer whose
+``feed_forward`` is None has the first half only; a weight stored for the norm of the missing half is read past.
 """
 from __future__ import annotations
+
+from dataclasses import replace
 
 from ..config.spec import LayerSpec
 from ..weights.tensors import TensorSpec
@@ -16,10 +19,12 @@ class PreNormBlock:
         names = self._names(layer)
         norms = self._norm_specs(layer)
         self.mixer_norm = part_class("norm", norms[0])(norms[0].params, names["mixer_norm"], runtime)
-        self.feed_forward_norm = part_class("norm", norms[1])(norms[1].params, names["feed_forward_norm"], runtime)
         self.mixer = part_class("mixer", layer.mixer)(layer.mixer.params, names["mixer"], runtime)
-        self.feed_forward = part_class("feed_forward", layer.feed_forward)(layer.feed_forward.params,
-                                                                           names["feed_forward"], runtime)
+        self.feed_forward_norm = self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = part_class("norm", norms[1])(norms[1].params, names["feed_forward_norm"], runtime)
+            self.feed_forward = part_class("feed_forward", layer.feed_forward)(layer.feed_forward.params,
+                                                                               names["feed_forward"], runtime)
 
     @staticmethod
     def _names(layer: LayerSpec) -> dict[str, str]:
@@ -38,8 +43,12 @@ class PreNormBlock:
         out: dict[str, TensorSpec] = {}
         norms = cls._norm_specs(layer)
         out.update(part_class("norm", norms[0]).expected_tensors(norms[0].params, names["mixer_norm"]))
-        out.update(part_class("norm", norms[1]).expected_tensors(norms[1].params, names["feed_forward_norm"]))
+        second = part_class("norm", norms[1]).expected_tensors(norms[1].params, names["feed_forward_norm"])
         out.update(part_class("mixer", layer.mixer).expected_tensors(layer.mixer.params, names["mixer"]))
+        if layer.feed_forward is None:
+            out.update({name: replace(spec, optional=True) for name, spec in second.items()})
+            return out
+        out.update(second)
         out.update(part_class("feed_forward", layer.feed_forward).expected_tensors(layer.feed_forward.params,
                                                                                    names["feed_forward"]))
         return out
@@ -51,7 +60,7 @@ class PreNormBlock:
 
     def parts(self) -> tuple:
         """The parts this block runs in a step."""
-        return (self.mixer_norm, self.feed_forward_norm, self.mixer, self.feed_forward)
+        return tuple(part for part in (self.mixer_norm, self.feed_forward_norm, self.mixer, self.feed_forward) if part is not None)
 
     @property
     def graph_safe(self) -> bool:
@@ -72,5 +81,7 @@ class PreNormBlock:
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         x = self._normed(self.mixer_norm, stream, self.mixer)
         stream.add(self.mixer.forward(x, ctx, cache))
+        if self.feed_forward is None:
+            return
         x = self._normed(self.feed_forward_norm, stream, self.feed_forward)
         stream.add(self.feed_forward.forward(x, ctx))

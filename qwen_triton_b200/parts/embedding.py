@@ -1,6 +1,6 @@
 """Token embedding into the float residual stream, and the output head.
 
-Embedding: row gather (qwen_triton/modules/embedding.py:9-25).  Head: logits = h W^T without bias,
+Embedding: row gather (qwen_triton/modules/embedding.py:9-25), times the parameter ``scale`` (default 1) in float.  Head: logits = h W^T without bias,
 W being the embedding table itself when tied (qwen_triton/models/core.py:259-263,364); logits are
 returned in float.
 """
@@ -20,6 +20,7 @@ class TokenEmbedding:
 
     def __init__(self, params, vocab_size: int, hidden_size: int, runtime: Runtime) -> None:
         self.name = params["name"]
+        self.scale = float(params.get("scale", 1.0))
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
         self.runtime = runtime
         self.table: torch.Tensor | None = None
@@ -32,7 +33,7 @@ class TokenEmbedding:
         self.table = source(self.name).to(device=self.runtime.device, dtype=self.runtime.dtype).contiguous()
 
     def forward(self, token_ids: torch.Tensor, residual: torch.Tensor) -> None:
-        kernels.embedding(residual, self.table, token_ids)
+        kernels.embedding(residual, self.table, token_ids, self.scale)
 
 
 @register_head("linear_head")

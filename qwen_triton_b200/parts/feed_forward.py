@@ -13,7 +13,7 @@ import torch
 from ..ops import kernels
 from ..ops.kernels import GemmOut
 from ..weights.tensors import TensorSpec
-from .base import DeferredProduct, Runtime, register_feed_forward
+from .base import DeferredProduct, Runtime, register_feed_forward, to_device
 from .linear import Linear
 
 
@@ -68,3 +68,76 @@ class GatedMLP:
         # few tokens: the down projection is left to the norm behind it, which launches it with the residual addition
         # (and its own preparation) in the product's epilogue
         return DeferredProduct(self.down, act) if self.down.fusable(tokens) else self.down(act)
+
+
+@register_feed_forward("table_experts")
+class TableExperts:
+    """A set of small two-matrix feed-forward layers ("experts"), down_e(act(up_e(x))) without biases, of which every
+    token runs the ``top`` that an integer table [vocab, top] names for its token id; their outputs are summed with
+    the weight ``pair_weight`` each (default 1 / top, the mean).  There is no learned router: the choice depends on
+    the token id alone, so it is read on the device from the step's token ids and a step launches the same kernels
+    whatever the tokens are.
+
+    Parameters: ``hidden_size``, ``expert_size`` (width of an expert's middle), ``experts``, ``top``, ``vocab_size``,
+    ``activation`` (one of ``kernels.ACTIVATIONS``), and the tensor-name pieces ``table``, ``expert`` (a format of the
+    expert's number), ``up``, ``down``, ``weight_suffix``.
+    """
+
+    graph_safe = True
+
+    def __init__(self, params, prefix: str, runtime: Runtime) -> None:
+        self.prefix = prefix
+        self.runtime = runtime
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["expert_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.vocab = int(params["vocab_size"])
+        self.activation = params.get("activation", "gelu")
+        if self.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"{prefix}: activation {self.activation!r} is not one of {sorted(kernels.ACTIVATIONS)}")
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"{prefix}: {self.top} experts per token out of {self.experts}")
+        self.pair_weight = float(params.get("pair_weight", 1.0 / self.top))
+        self.params = dict(params)
+        self.up = self.down = self.table = None
+        ws = runtime.workspace
+        ws.declare("experts.mid", runtime.max_step_tokens * self.top * self.inter, runtime.dtype)
+        ws.declare("experts.out", runtime.max_step_tokens * self.hidden, torch.float32)
+
+    @staticmethod
+    def _tensor_names(params, prefix: str) -> tuple[str, list[tuple[str, str]]]:
+        suffix = str(params.get("weight_suffix", ".weight"))
+        expert = str(params.get("expert", "experts.{}"))
+        up, down = params.get("up", "up"), params.get("down", "down")
+        pairs = [(f"{prefix}.{expert.format(e)}.{up}{suffix}", f"{prefix}.{expert.format(e)}.{down}{suffix}")
+                 for e in range(int(params["experts"]))]
+        return f"{prefix}.{params.get('table', 'table')}", pairs
+
+    @classmethod
+    def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
+        hidden, inter = int(params["hidden_size"]), int(params["expert_size"])
+        table, pairs = cls._tensor_names(params, prefix)
+        out = {table: TensorSpec((int(params["vocab_size"]), int(params["top"])), role="table", table_high=int(params["experts"]))}
+        for up, down in pairs:
+            out[up] = TensorSpec((inter, hidden), init_std=0.05)
+            out[down] = TensorSpec((hidden, inter), init_std=0.05)
+        return out
+
+    def load(self, source) -> None:
+        table, pairs = self._tensor_names(self.params, self.prefix)
+        dtype, device = self.runtime.dtype, self.runtime.device
+        self.up = torch.stack([source(up).to(device=device, dtype=dtype) for up, _ in pairs]).contiguous()
+        self.down = torch.stack([source(down).to(device=device, dtype=dtype) for _, down in pairs]).contiguous()
+        table = source(table)
+        if int(table.min()) < 0 or int(table.max()) >= self.experts:
+            raise ValueError(f"{self.prefix}: the table names experts outside 0..{self.experts - 1}")
+        self.table = to_device(table, torch.int32, device)
+
+    def forward(self, x, ctx) -> GemmOut:
+        tokens = x.shape[0]
+        ws = self.runtime.workspace
+        out = ws.view("experts.out", tokens, self.hidden)
+        mid = ws.view("experts.mid", tokens * self.top, self.inter)
+        kernels.experts_by_pair(x, ctx.token_ids, self.table, self.up, self.down, mid, out, self.activation, self.pair_weight)
+        return GemmOut(out.view(1, tokens, self.hidden))

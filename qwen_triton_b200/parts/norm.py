@@ -2,6 +2,10 @@
 
 y = x * rsqrt(mean(x^2) + eps) * w in float with one rounding at the end, as in the reference
 (qwen_triton/kernels/rmsnorm.py:35-42; module qwen_triton/modules/norms.py:9-21).
+
+Parameters beyond ``size`` and ``eps``: ``groups`` (default 1) splits a row into that many equal consecutive parts,
+each divided by its own root mean square, the weight spanning the whole row; ``suffix`` (default ".weight") is what
+the weight's tensor name adds to the norm's name.
 """
 from __future__ import annotations
 
@@ -16,11 +20,16 @@ from .base import ResidualStream, Runtime, register_norm, to_device
 @register_norm("rmsnorm")
 class RMSNorm:
     graph_safe = True
-    offers_scaled_rows = True      # apply(..., lazy=True) may hand on ScaledRows
 
     def __init__(self, params, name: str, runtime: Runtime) -> None:
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.groups = int(params.get("groups", 1))
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"{name}: {self.groups} groups do not divide a width of {self.size}")
+        # apply(..., lazy=True) may hand on ScaledRows: one factor per row, so only where the row is one group
+        self.offers_scaled_rows = self.groups == 1
+        self.tensor = name + str(params.get("suffix", ".weight"))
         self.name = name
         self.runtime = runtime
         self.weight: torch.Tensor | None = None
@@ -29,10 +38,10 @@ class RMSNorm:
 
     @classmethod
     def expected_tensors(cls, params, name: str) -> dict[str, TensorSpec]:
-        return {f"{name}.weight": TensorSpec((int(params["size"]),), role="vector", init_std=0.1, init_mean=1.0)}
+        return {name + str(params.get("suffix", ".weight")): TensorSpec((int(params["size"]),), role="vector", init_std=0.1, init_mean=1.0)}
 
     def load(self, source) -> None:
-        self.weight = to_device(source(f"{self.name}.weight"), torch.float32, self.runtime.device)
+        self.weight = to_device(source(self.tensor), torch.float32, self.runtime.device)
 
     def apply(self, stream: ResidualStream, rows: torch.Tensor | None = None, lazy: bool = False):
         """Fold the pending delta into the stream and return the normed rows.
@@ -51,7 +60,7 @@ class RMSNorm:
             count = stream.residual.shape[0]
             if not deferred.linear.fusable(count):
                 stream.pending = deferred.run()
-            elif rows is None and lazy:
+            elif rows is None and lazy and self.offers_scaled_rows:
                 xw = ws.view("normed", count, self.size)
                 sq = ws.view("normed.sq", -(-self.size // 128), count)
                 return deferred.linear.into_residual(deferred.x, stream.residual, self.weight, self.eps, xw, sq)
@@ -59,7 +68,7 @@ class RMSNorm:
                 deferred.linear.into_residual(deferred.x, stream.residual)
         count = stream.residual.shape[0] if rows is None else rows.shape[0]
         out = ws.view("normed", count, self.size)
-        kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out, rows)
+        kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out, rows, self.groups)
         if rows is None:
             stream.pending = None
         return out

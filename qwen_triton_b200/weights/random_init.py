@@ -72,7 +72,18 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype,
     """Draw one tensor in float32, round it once to ``store_dtype`` (what a model folder would hold; by default
     ``dtype``) and return it as ``dtype``."""
     if spec.role == "table":
-        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        if spec.table_high <= 0:
+            return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        # a row's numbers are the places of its smallest keys among ``table_high`` drawn ones: distinct, and the same
+        # bits wherever they are drawn (equal keys, should they occur, keep their order)
+        rows = 1
+        for dim in spec.shape[:-1]:
+            rows *= dim
+        if spec.shape[-1] > spec.table_high:
+            raise ValueError(f"{name}: rows of {spec.shape[-1]} distinct numbers below {spec.table_high} do not exist")
+        keys = standard_normal(_tensor_seed(seed, name), 0, rows * spec.table_high, device).view(rows, spec.table_high)
+        order = torch.sort(keys, dim=1, stable=True).indices[:, :spec.shape[-1]]
+        return order.to(torch.int32).reshape(spec.shape).contiguous()
     count = 1
     for dim in spec.shape:
         count *= dim

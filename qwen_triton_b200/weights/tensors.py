@@ -15,7 +15,8 @@ class TensorSpec:
     * ``vector``  a small per-channel tensor such as a norm weight; kept in
       float32, which holds bfloat16 and 32-bit files alike without loss;
       random: ``init_mean`` + N(0, ``init_std``).
-    * ``table``   an integer table; kept as int32; random: zeros.
+    * ``table``   an integer table; kept as int32; random: zeros, or with ``table_high`` = n > 0 every row
+      (last dim) holds distinct numbers below n.
     """
 
     shape: tuple[int, ...]
@@ -23,3 +24,4 @@ class TensorSpec:
     init_std: float = 0.02
     init_mean: float = 0.0
     optional: bool = False   # e.g. lm_head.weight of a tied model: read if present, never required
+    table_high: int = 0      # role "table": random rows of distinct integers in [0, table_high)
