@@ -129,4 +129,101 @@ extern "C" int qt_experts_by_pair(const void* x, const int* token_ids, const int
     });
 }
 
+// ----------------------------------------------------------------------------- many tokens: pairs ordered by expert
+// Routing for the tiled products (experts_tc.cu).  One block: count the pairs of every expert, give every expert a
+// run of rows padded to whole tiles of `tile_rows`, and give every pair a row in its expert's run.
+//   pair_row[pair]     the pair's row in the ordered buffers
+//   row_token[row]     the token whose (normed) input the row holds, -1 for padding
+//   tile_expert[tile]  the expert of the tile's rows, -1 for tiles beyond the last run
+// Which row of its run a pair gets depends on the order the threads arrive in; a row's results do not depend on where
+// it lies, so the output does not either.
+__global__ void __launch_bounds__(1024) expert_route_kernel(const ExpertParams p, int* __restrict__ pair_row, int* __restrict__ row_token,
+                                                            int* __restrict__ tile_expert, int tile_rows, int max_tiles) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int route_smem[];
+    int* counts = route_smem;                 // [E]
+    int* starts = counts + p.experts;         // [E + 1], in rows
+    int* cursor = starts + p.experts + 1;     // [E]
+    const int pairs = p.n_tokens * p.top;
+    for (int e = threadIdx.x; e < p.experts; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x) atomicAdd(&counts[expert_of(p, pair / p.top, pair % p.top)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < p.experts; ++e) {
+            starts[e] = at;
+            at += (counts[e] + tile_rows - 1) / tile_rows * tile_rows;
+        }
+        starts[p.experts] = at;
+    }
+    __syncthreads();
+    const int used_tiles = starts[p.experts] / tile_rows;
+    for (int e = threadIdx.x; e < p.experts; e += blockDim.x)
+        for (int tile = starts[e] / tile_rows; tile < starts[e + 1] / tile_rows; ++tile) tile_expert[tile] = e;
+    for (int tile = used_tiles + threadIdx.x; tile < max_tiles; tile += blockDim.x) tile_expert[tile] = -1;
+    for (int row = threadIdx.x; row < max_tiles * tile_rows; row += blockDim.x) row_token[row] = -1;
+    __syncthreads();
+    for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x) {
+        const int e = expert_of(p, pair / p.top, pair % p.top);
+        const int row = starts[e] + atomicAdd(&cursor[e], 1);
+        pair_row[pair] = row;
+        row_token[row] = pair / p.top;
+    }
+}
+
+// ordered[row, :] = x[row_token[row], :] (zeros for padding rows).  One block per row, 16 bytes per thread and turn.
+__global__ void expert_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ row_token, uint4* __restrict__ ordered, int chunks) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x, token = row_token[row];
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x)
+        ordered[(size_t)row * chunks + c] = token >= 0 ? x[(size_t)token * chunks + c] : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// out[t, :] = pair_weight * sum_k y[pair_row[t * top + k], :], in float, in the order of k.
+template <typename T>
+__global__ void expert_combine_kernel(const T* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ out, int top, int width,
+                                      float pair_weight) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc += to_float(y[(size_t)pair_row[t * top + k] * width + c]);
+        out[(size_t)t * width + c] = acc * pair_weight;
+    }
+}
+
+extern "C" int qt_experts_route(const void* x, const int* token_ids, const int* table, void* ordered, int* pair_row, int* row_token,
+                                int* tile_expert, int n_tokens, int vocab, int top, int experts, int width, int tile_rows, int max_tiles,
+                                void* stream) {
+    int rc = check_experts("experts_route", n_tokens, vocab, top, experts, width, 1, 0);
+    if (rc) return rc;
+    if (n_tokens == 0) return QT_OK;
+    QT_REQUIRE(width % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)ordered % 16 == 0, "experts_route: rows of 16-byte pieces are needed (width=%d)", width);
+    QT_REQUIRE(tile_rows > 0 && (long long)max_tiles * tile_rows >= (long long)n_tokens * top, "experts_route: %d tiles of %d rows do not hold the pairs", max_tiles, tile_rows);
+    QT_REQUIRE((3 * (size_t)experts + 1) * sizeof(int) <= 48 * 1024, "experts_route: %d experts are too many for one block's counters", experts);
+    ExpertParams p{x, token_ids, table, nullptr, nullptr, nullptr, nullptr, n_tokens, vocab, top, experts, width, 1, 0, 0.f};
+    cudaStream_t s = (cudaStream_t)stream;
+    launch_kernel(expert_route_kernel, dim3(1), dim3(1024), (3 * (size_t)experts + 1) * sizeof(int), s, p, pair_row, row_token, tile_expert, tile_rows, max_tiles);
+    QT_CHECK_LAUNCH("expert_route");
+    launch_kernel(expert_gather_kernel, dim3(max_tiles * tile_rows), dim3(128), 0, s, (const uint4*)x, (const int*)row_token, (uint4*)ordered, width / 8);
+    QT_CHECK_LAUNCH("expert_gather");
+    return QT_OK;
+}
+
+extern "C" int qt_experts_combine(const void* y, int dtype, const int* pair_row, float* out, int n_tokens, int top, int width, float pair_weight,
+                                  void* stream) {
+    QT_REQUIRE(n_tokens >= 0 && top > 0 && width > 0, "experts_combine: bad sizes T=%d top=%d width=%d", n_tokens, top, width);
+    if (n_tokens == 0) return QT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    return QT_DISPATCH_DTYPE(dtype, "experts_combine", {
+        launch_kernel(expert_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, s, (const T*)y, pair_row, out, top, width, pair_weight);
+        QT_CHECK_LAUNCH("expert_combine");
+        return QT_OK;
+    });
+}
+
 QT_DEFINE_LAST_ERROR(experts)

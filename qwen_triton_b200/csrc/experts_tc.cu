@@ -1,0 +1,191 @@
+// The two products of table-chosen experts for many tokens, on the fifth-generation tensor cores.
+//
+// The rows (token, expert pairs) arrive ordered by expert, every expert's run padded to whole tiles of 128 rows
+// (experts.cu), so a tile's rows all take one expert's weight: Y[rows of the tile, :] = X[rows, :] * W[e]^T with e read
+// from `tile_expert`.  A tile beyond the last run (-1) leaves at once.  The weights of all experts are one matrix
+// [E * N, K]; a weight tile of 128 rows that reaches past its expert's N rows reads the next expert's (or zeros past
+// the end), and the epilogue drops those columns.
+//
+// The rows are the MMA's M (128 per block), the weight rows its N (128): a thread of the epilogue holds 32 consecutive
+// output features of one row per tcgen05.ld, applies the activation where asked and stores 16 bytes at a time.
+// TMA (128-byte swizzle) stages 64-element K slices in a ring; one elected thread issues tcgen05.mma, the
+// accumulator lives in tensor memory.  Warp roles and the bounded waits are those of gemm_tc.cu.
+#include "tc_common.cuh"
+
+using namespace qt;
+using namespace qt_tc;
+
+namespace {
+
+constexpr int BM = 128;        // rows per tile = MMA M
+constexpr int BN = 128;        // weight rows per tile = MMA N
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int STAGES = 3;      // 96 KB: two blocks share an SM, one's epilogue runs under the other's MMAs
+
+__device__ __forceinline__ void store8(float* dst, const float (&f)[8]) {
+    reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const float (&f)[8]) {
+    uint4 packed;
+    __nv_bfloat162 h;
+    h = __floats2bfloat162_rn(f[0], f[1]); packed.x = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(f[2], f[3]); packed.y = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(f[4], f[5]); packed.z = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(f[6], f[7]); packed.w = *reinterpret_cast<uint32_t*>(&h);
+    *reinterpret_cast<uint4*>(dst) = packed;
+}
+
+template <typename TO, bool ACT>
+__global__ void __launch_bounds__(THREADS) expert_gemm_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                              const __grid_constant__ CUtensorMap map_w, TO* __restrict__ out,
+                                                              const int* __restrict__ tile_expert, int n_out, int kb_total,
+                                                              int w_tiles, int act, int* status) {
+    // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N = 128, M = 128
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    extern __shared__ uint8_t smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();                                                    // the routing and the rows come from the kernels before
+    const int x_tile = blockIdx.x / w_tiles, w_tile = blockIdx.x % w_tiles;
+    const int expert = tile_expert[x_tile];
+    if (expert < 0) return;                                        // the whole block: nothing is set up yet
+
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                  // swizzled tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw + (base - raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE_BYTES);
+    const uint32_t full0 = base + STAGES * STAGE_BYTES, empty0 = full0 + 8 * STAGES, tmem_full = empty0 + 8 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int x0 = x_tile * BM, w0 = expert * n_out + w_tile * BN;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensor_map(&map_w);
+        prefetch_tensor_map(&map_x);
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            for (int i = 0; i < kb_total; ++i) {
+                if (i >= STAGES && !mbar_wait(empty0 + 8 * s, phase ^ 1u, status, 1)) break;
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                const uint32_t dst = base + s * STAGE_BYTES;
+                tma_load_2d(dst, &map_x, full0 + 8 * s, i * BK, x0);
+                tma_load_2d(dst + A_BYTES, &map_w, full0 + 8 * s, i * BK, w0);
+                if (++s == STAGES) { s = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint64_t a_desc0 = operand_desc(base), b_desc0 = operand_desc(base + A_BYTES);
+            int s = 0;
+            uint32_t phase = 0;
+            for (int i = 0; i < kb_total; ++i) {
+                if (!mbar_wait(full0 + 8 * s, phase, status, 2)) break;
+                tc_fence_after();
+                const uint64_t a_desc = a_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+                const uint64_t b_desc = b_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)      // 32 bytes further along K inside the swizzled row
+                    umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);
+                if (++s == STAGES) { s = 0; phase ^= 1u; }
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        const int quarter = warp & 3;                      // the accumulator lanes this warp may read
+        const bool ready = mbar_wait(tmem_full, 0, status, 3);
+        tc_fence_after();
+        TO* dst = out + (size_t)(x0 + quarter * 32 + lane) * n_out;
+        if (ready) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                const int f0 = w_tile * BN + c;
+                if (f0 >= n_out) break;                    // the same for the whole warp
+                uint32_t v[32];
+                tmem_load32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    if (f0 + 8 * g >= n_out) break;        // n_out is a multiple of 8
+                    float f[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float a = __uint_as_float(v[8 * g + j]);
+                        f[j] = ACT ? gate_activation<false>(a, act) : a;
+                    }
+                    store8(dst + f0 + 8 * g, f);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*(volatile int*)status != 0) {                     // a wait gave up: let copies in flight land before the block leaves
+        const unsigned long long t0 = global_timer();
+        while (global_timer() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+template <typename TO, bool ACT>
+int launch(const CUtensorMap& map_x, const CUtensorMap& map_w, TO* out, const int* tile_expert, int max_tiles, int n_out, int kb_total,
+           int act, int* status, cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(expert_gemm_kernel<TO, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "expert_gemm: cannot raise shared memory: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    const int w_tiles = (n_out + BN - 1) / BN;
+    launch_kernel(expert_gemm_kernel<TO, ACT>, dim3((unsigned)(max_tiles * w_tiles)), dim3(THREADS), smem, stream, map_x, map_w, out, tile_expert,
+                  n_out, kb_total, w_tiles, act, status);
+    QT_CHECK_LAUNCH("expert_gemm");
+    return QT_OK;
+}
+
+}  // namespace
+
+// out [max_tiles * 128, n_out] = act?(x [max_tiles * 128, K] * w[tile's expert] [n_out, K]^T), w being [experts * n_out, K].
+// `act` < 0: no activation.  Codes in `status`: as in gemm_tc.cu (1 = the TMA producer, 2 = the MMA issuer, 3 = the epilogue).
+extern "C" int qt_expert_gemm(const void* x, const void* w, void* out, int out_dtype, const int* tile_expert, int max_tiles, int experts,
+                              int n_out, int K, int act, int* status, void* stream) {
+    QT_REQUIRE(max_tiles > 0 && experts > 0 && n_out > 0 && K > 0, "expert_gemm: bad sizes tiles=%d E=%d N=%d K=%d", max_tiles, experts, n_out, K);
+    QT_REQUIRE(K % 8 == 0 && n_out % 8 == 0, "expert_gemm: K=%d and N=%d must be multiples of 8 (16-byte rows for TMA and for the stores)", K, n_out);
+    QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0), "expert_gemm: operands must be 16-byte aligned");
+    QT_REQUIRE(act < QT_ACT_COUNT, "expert_gemm: unknown activation code %d", act);
+    QT_REQUIRE(status != nullptr && tile_expert != nullptr, "expert_gemm: a status word and the tiles' experts are required");
+    QT_REQUIRE((long long)max_tiles * ((n_out + BN - 1) / BN) < (1ll << 31), "expert_gemm: too many tiles for one launch");
+    CUtensorMap map_x, map_w;
+    int rc = tensor_map(&map_x, x, (uint64_t)max_tiles * BM, (uint64_t)K, BM);
+    if (rc) return rc;
+    rc = tensor_map(&map_w, w, (uint64_t)experts * n_out, (uint64_t)K, BN);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int kb_total = (K + BK - 1) / BK;
+    if (out_dtype == QT_BF16 && act >= 0) return launch<__nv_bfloat16, true>(map_x, map_w, (__nv_bfloat16*)out, tile_expert, max_tiles, n_out, kb_total, act, status, s);
+    if (out_dtype == QT_BF16) return launch<__nv_bfloat16, false>(map_x, map_w, (__nv_bfloat16*)out, tile_expert, max_tiles, n_out, kb_total, 0, status, s);
+    if (out_dtype == QT_F32 && act < 0) return launch<float, false>(map_x, map_w, (float*)out, tile_expert, max_tiles, n_out, kb_total, 0, status, s);
+    QT_FAIL(QT_ERR_ARG, "expert_gemm: output type %d%s is not offered", out_dtype, act >= 0 ? " with an activation" : "");
+}
+
+QT_DEFINE_LAST_ERROR(experts_tc)

@@ -43,6 +43,12 @@ _SIGNATURES = {
     "experts": {
         "qt_experts_by_pair": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                _c_int, _c_int, _c_int, _c_float, _c_ptr],
+        "qt_experts_route": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                             _c_int, _c_ptr],
+        "qt_experts_combine": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+    },
+    "experts_tc": {
+        "qt_expert_gemm": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     },
     "attention_mma": {
         "qt_attention_decode_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
@@ -511,6 +517,52 @@ def experts_by_pair(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tenso
     _call("experts", "qt_experts_by_pair", _ptr(x), _ptr(token_ids), _ptr(table), _ptr(up), _ptr(down), _ptr(mid), _ptr(out),
           _code(x, "x"), tokens, table.shape[0], top, experts, width, ff, activation_code(activation), float(pair_weight),
           _stream(), launches=2)
+
+
+EXPERT_TILE_ROWS = 128      # rows of one tile of the tiled expert products (the MMA's M)
+
+
+def expert_tiles(pairs: int, experts: int) -> int:
+    """Tiles that hold ``pairs`` rows ordered by expert, however they fall: every expert's run ends in a tile of its own."""
+    return pairs // EXPERT_TILE_ROWS + experts
+
+
+def experts_tiled_supported(x: torch.Tensor, up: torch.Tensor) -> bool:
+    """The tiled expert products take bfloat16 with widths that are multiples of 8 (16-byte rows)."""
+    return x.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and up.shape[1] % 8 == 0 and up.shape[2] % 8 == 0
+
+
+def experts_tiled(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
+                  ordered: torch.Tensor, mid: torch.Tensor, y: torch.Tensor, route: torch.Tensor, out: torch.Tensor,
+                  activation: str, pair_weight: float) -> None:
+    """The same result as ``experts_by_pair`` for many tokens: the (token, expert) pairs are ordered by expert on the
+    device, each expert's run padded to whole tiles of 128 rows, and both products run tile by tile on the tensor
+    cores.  Scratch: ``ordered`` [rows, width], ``mid`` [rows, ff], ``y`` [rows, width] (bfloat16) with
+    rows = expert_tiles(T * top, E) * 128, and ``route`` (int32, T * top + rows + rows / 128 words)."""
+    tokens, width = x.shape
+    experts, ff = up.shape[0], up.shape[1]
+    top = table.shape[1]
+    tiles = expert_tiles(tokens * top, experts)
+    rows = tiles * EXPERT_TILE_ROWS
+    _need(x, "x", torch.bfloat16)
+    _need(token_ids, "token_ids", torch.int32, (tokens,))
+    _need(table, "table", torch.int32)
+    _need(up, "up", torch.bfloat16, (experts, ff, width))
+    _need(down, "down", torch.bfloat16, (experts, width, ff))
+    _need(ordered, "ordered", torch.bfloat16, (rows, width))
+    _need(mid, "mid", torch.bfloat16, (rows, ff))
+    _need(y, "y", torch.bfloat16, (rows, width))
+    _need(route, "route", torch.int32, (tokens * top + rows + tiles,))
+    _need(out, "out", torch.float32, (tokens, width))
+    pair_row, row_token, tile_expert = route[:tokens * top], route[tokens * top:tokens * top + rows], route[tokens * top + rows:]
+    status = _status_word(x.device)
+    _call("experts", "qt_experts_route", _ptr(x), _ptr(token_ids), _ptr(table), _ptr(ordered), _ptr(pair_row), _ptr(row_token),
+          _ptr(tile_expert), tokens, table.shape[0], top, experts, width, EXPERT_TILE_ROWS, tiles, _stream(), launches=2)
+    _call("experts_tc", "qt_expert_gemm", _ptr(ordered), _ptr(up), _ptr(mid), BF16, _ptr(tile_expert), tiles, experts, ff, width,
+          activation_code(activation), _ptr(status), _stream())
+    _call("experts_tc", "qt_expert_gemm", _ptr(mid), _ptr(down), _ptr(y), BF16, _ptr(tile_expert), tiles, experts, width, ff,
+          -1, _ptr(status), _stream())
+    _call("experts", "qt_experts_combine", _ptr(y), BF16, _ptr(pair_row), _ptr(out), tokens, top, width, float(pair_weight), _stream())
 
 
 # ----------------------------------------------------------------------------- matrix product

@@ -70,6 +70,11 @@ class GatedMLP:
         return DeferredProduct(self.down, act) if self.down.fusable(tokens) else self.down(act)
 
 
+# Most (token, expert) pairs that run as matrix-vector passes, each streaming its expert's rows once; beyond, the pairs
+# are ordered by expert and the products run in tiles on the tensor cores.
+_PAIRS_BY_PAIR = 64
+
+
 @register_feed_forward("table_experts")
 class TableExperts:
     """A set of small two-matrix feed-forward layers ("experts"), down_e(act(up_e(x))) without biases, of which every
@@ -102,8 +107,18 @@ class TableExperts:
         self.params = dict(params)
         self.up = self.down = self.table = None
         ws = runtime.workspace
-        ws.declare("experts.mid", runtime.max_step_tokens * self.top * self.inter, runtime.dtype)
         ws.declare("experts.out", runtime.max_step_tokens * self.hidden, torch.float32)
+        # many tokens in bfloat16: the pairs ordered by expert in tiles of rows, both products on the tensor cores
+        self.tiled = runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0
+        pairs = runtime.max_step_tokens * self.top
+        rows = pairs
+        if self.tiled:
+            tiles = kernels.expert_tiles(pairs, self.experts)
+            rows = tiles * kernels.EXPERT_TILE_ROWS
+            ws.declare("experts.ordered", rows * self.hidden, runtime.dtype)
+            ws.declare("experts.y", rows * self.hidden, runtime.dtype)
+            ws.declare("experts.route", pairs + rows + tiles, torch.int32)
+        ws.declare("experts.mid", rows * self.inter, runtime.dtype)
 
     @staticmethod
     def _tensor_names(params, prefix: str) -> tuple[str, list[tuple[str, str]]]:
@@ -138,6 +153,14 @@ class TableExperts:
         tokens = x.shape[0]
         ws = self.runtime.workspace
         out = ws.view("experts.out", tokens, self.hidden)
-        mid = ws.view("experts.mid", tokens * self.top, self.inter)
-        kernels.experts_by_pair(x, ctx.token_ids, self.table, self.up, self.down, mid, out, self.activation, self.pair_weight)
+        pairs = tokens * self.top
+        if self.tiled and pairs > _PAIRS_BY_PAIR:
+            tiles = kernels.expert_tiles(pairs, self.experts)
+            rows = tiles * kernels.EXPERT_TILE_ROWS
+            kernels.experts_tiled(x, ctx.token_ids, self.table, self.up, self.down, ws.view("experts.ordered", rows, self.hidden),
+                                  ws.view("experts.mid", rows, self.inter), ws.view("experts.y", rows, self.hidden),
+                                  ws.view("experts.route", pairs + rows + tiles), out, self.activation, self.pair_weight)
+        else:
+            mid = ws.view("experts.mid", pairs, self.inter)
+            kernels.experts_by_pair(x, ctx.token_ids, self.table, self.up, self.down, mid, out, self.activation, self.pair_weight)
         return GemmOut(out.view(1, tokens, self.hidden))
