@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the Qwen3-8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl b200|reference] [--temperature T]
-    python bench.py --workload 0.6b-unequal | 32b-long
+    python bench.py --workload 0.6b-unequal | 32b-long | lederax-layers
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from a 2,048-token cache,
 timed on the device over the decode steps (step function plus greedy sampling kernel, tokens given
@@ -16,7 +16,10 @@ cap.  ``steps`` is the number of steps actually timed, ``config.steps_requested`
 
 ``--workload`` runs one of the secondary workloads instead: ``0.6b-unequal`` (Qwen3-0.6B shape, 16 prompts with
 lengths uniform in 64..2,048, 128 new tokens each, through ``generate``), ``32b-long`` (Qwen3-32B shape, batch
-64 decoded from 2,048 to 4,096 positions, with the roofline fraction in windows of 64 steps near 2,048, 3,072 and 4,096).
+64 decoded from 2,048 to 4,096 positions, with the roofline fraction in windows of 64 steps near 2,048, 3,072 and 4,096),
+``lederax-layers`` (four layers of the Lederax design at three sets of sizes that resemble a real model's, beside a Qwen3
+dense model of the same width, heads, window and as many weights read per token: prefill of one prompt and one-token steps
+at batch 8 and 64, each with its share of the measured peaks).
 """
 from __future__ import annotations
 
@@ -50,7 +53,7 @@ def parse_args():
     parser.add_argument("--no-prefill", action="store_true")
     parser.add_argument("--min-seconds", type=float, default=2.0, help="a timed region lasts at least this long")
     parser.add_argument("--temperature", type=float, default=0.0, help="sampling temperature of the end-to-end run (0: greedy)")
-    parser.add_argument("--workload", default=None, choices=["0.6b-unequal", "32b-long"])
+    parser.add_argument("--workload", default=None, choices=["0.6b-unequal", "32b-long", "lederax-layers"])
     return parser.parse_args()
 
 
@@ -332,9 +335,78 @@ def run_b200(args) -> dict:
     return line
 
 
+# ----------------------------------------------------------------------------- the Lederax design beside the dense model
+LEDERAX_SIZES = (
+    # name, width, heads, kv heads, head size, window, experts, top, expert width
+    ("w2048-h16-win1024-e32x1024-top2", 2048, 16, 4, 128, 1024, 32, 2, 1024),
+    ("w4096-h32-win4096-e16x2048-top2", 4096, 32, 8, 128, 4096, 16, 2, 2048),
+    ("w1024-h16-d64-win512-e8x4096-top1", 1024, 16, 16, 64, 512, 8, 1, 4096),
+)
+
+
+def run_lederax_layers(args) -> dict:
+    """Prefill and one-token steps of a few Lederax layers at sizes that resemble a real model's, and of the Qwen3
+    dense layers that come closest: same width, heads, head size, window and vocabulary, and a gated feed-forward
+    that reads as many weights per token as the chosen experts do (3 h i = 2 h ff top)."""
+    import torch
+
+    from qwen_triton_b200 import QwenB200ForCausalLM, config_from_dict
+
+    peak, peak_source = peaks()
+    layers, vocab, prompt_len = args.layers or 4, 32768, args.prompt_len
+    out = []
+    for name, width, heads, kv_heads, dim, window, experts, top, ff in LEDERAX_SIZES:
+        inter = max(64, round(2 * ff * top / 3 / 64) * 64)
+        lederax = {"architecture": "Lederax", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+                   "norm": {"eps": 1e-6, "groups": 4},
+                   "layers": [{"type": "attention",
+                               "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                         "mask": {"size": window}, "v_mix": True},
+                               "mlp": {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}}] * layers}
+        dense = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": vocab, "hidden_size": width,
+                 "intermediate_size": inter, "num_hidden_layers": layers, "num_attention_heads": heads,
+                 "num_key_value_heads": kv_heads, "head_dim": dim, "max_position_embeddings": 32768,
+                 "use_sliding_window": True, "sliding_window": window, "max_window_layers": 0}
+        attention = width * (heads + 2 * kv_heads) * dim + heads * dim * width
+        entry = {"size": name, "layers": layers, "dense_intermediate": inter}
+        for label, raw, mlp_read, mlp_flops in (("lederax", lederax, lambda rows: 2 * width * ff * min(experts, rows * top), 2 * width * ff * top),
+                                                ("dense", dense, lambda rows: 3 * width * inter, 3 * width * inter)):
+            model = QwenB200ForCausalLM.from_config(config_from_dict(raw), seed=1, dtype="bf16",
+                                                    max_tokens=64 * (prompt_len + 512), max_seq_len=prompt_len + 512,
+                                                    max_step_tokens=max(4096, prompt_len), chunk_tokens=prompt_len)
+            result = {}
+            ms = time_prefill(model, prompt_len, vocab)
+            flops = 2 * prompt_len * (layers * (attention + mlp_flops) + vocab * width / prompt_len) \
+                + 4 * layers * heads * dim * prompt_len * min(window, prompt_len / 2)
+            result["prefill"] = {"tokens": prompt_len, "ms": round(ms, 3), "tokens_per_s": round(prompt_len * 1e3 / ms),
+                                 "tensor_fraction": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
+            for batch in (8, 64):
+                prompts = random_prompts(batch, prompt_len, vocab, 300 + batch)
+                ms, launches, clocks, context, steps = time_decode(model, prompts, args.steps, args.warmup, vocab,
+                                                                   args.min_seconds / 4, 256)
+                read = 2 * (layers * (attention + mlp_read(batch)) + vocab * width) \
+                    + batch * min(window, context) * layers * 2 * kv_heads * dim * 2
+                result[f"decode_batch{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch * 1e3 / ms),
+                                                   "launches_per_step": round(launches / steps, 1), "steps": steps,
+                                                   "hbm_fraction": round(read / (ms * 1e-3) / (peak["hbm_gbs"] * 1e9), 4),
+                                                   "clocks": clocks}
+            entry[label] = result
+            print(f"[bench] {name} {label}: " + json.dumps({k: {a: b for a, b in v.items() if a != 'clocks'} for k, v in result.items()}),
+                  file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+        out.append(entry)
+    return {"workload": args.workload, "impl": "b200", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+            "config": {"prompt_len": prompt_len, "layers": layers, "vocab": vocab, "peaks": peak_source,
+                       "l2": "weights and caches of a step exceed L2 at every size but the smallest"},
+            "sizes": out}
+
+
 # ----------------------------------------------------------------------------- secondary workloads
 def run_workload(args) -> dict:
     """BASELINE's secondary workloads as they are stated."""
+    if args.workload == "lederax-layers":
+        return run_lederax_layers(args)
     import torch
 
     from qwen_triton_b200 import QwenB200ForCausalLM, StepEntry, load_preset

@@ -97,10 +97,12 @@ extern "C" int qt_attention_decode_mma(const void* q, const void* k_cache, const
 extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const void* v_cache, void* out,
                                       const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
                                       int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
-                                      int n_splits, int warps, float* part_acc, float* part_ml, void* stream) {
+                                      int n_splits, int warps, float* part_acc, float* part_ml, const float* r1, const float* r2,
+                                      void* stream) {
     if (n_seqs == 0) return QT_OK;
     int rc = check("attention_decode_ws", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
     if (rc) return rc;
+    QT_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_decode_ws: the distance penalty needs both of its factors");
     QT_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode_ws: n_splits=%d", n_splits);
     QT_REQUIRE(warps >= 1 && warps <= WS_MAX_WARPS, "attention_decode_ws: %d warps per block (1 to %d)", warps, WS_MAX_WARPS);
     QT_REQUIRE(scale > 0.f, "attention_decode_ws: the score scale must be positive (the row maximum is taken before scaling)");
@@ -116,21 +118,26 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
     QT_REQUIRE(n_splits == 1 || cluster || (part_acc && part_ml), "attention_decode_ws: split results need scratch memory");
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, nullptr, nullptr, seq_len, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                n_splits, part_acc, part_ml, 2, cluster ? 1 : 0};
+                n_splits, part_acc, part_ml, 2, cluster ? 1 : 0, r1, r2};
     const size_t smem = rings + (cluster ? inboxes : 0);
     dim3 grid(n_splits, nkv * ((group + 15) / 16), n_seqs), block(32 * warps);
     cudaStream_t s = (cudaStream_t)stream;
-#define QT_LAUNCH_WS(DMAX, EXACT)                                                                                        \
+#define QT_LAUNCH_WS(DMAX, EXACT, PEN)                                                                                   \
     do {                                                                                                                 \
         static bool ok = false;                                                                                          \
-        if (!ok) { rc = raise_smem(attention_decode_ws_kernel<DMAX, EXACT>, 227 * 1024, "attention_decode_ws"); if (rc) return rc; ok = true; } \
-        if (cluster) launch_kernel_cluster(attention_decode_ws_kernel<DMAX, EXACT>, grid, block, smem, s, (unsigned)n_splits, p); \
-        else launch_kernel(attention_decode_ws_kernel<DMAX, EXACT>, grid, block, smem, s, p);                             \
+        if (!ok) { rc = raise_smem(attention_decode_ws_kernel<DMAX, EXACT, PEN>, 227 * 1024, "attention_decode_ws"); if (rc) return rc; ok = true; } \
+        if (cluster) launch_kernel_cluster(attention_decode_ws_kernel<DMAX, EXACT, PEN>, grid, block, smem, s, (unsigned)n_splits, p); \
+        else launch_kernel(attention_decode_ws_kernel<DMAX, EXACT, PEN>, grid, block, smem, s, p);                        \
     } while (0)
-    if (d == 128) QT_LAUNCH_WS(128, true);
-    else if (d == 64) QT_LAUNCH_WS(64, true);
-    else if (d < 64) QT_LAUNCH_WS(64, false);
-    else QT_LAUNCH_WS(128, false);
+    if (r1) {
+        if (d == 128) QT_LAUNCH_WS(128, true, true);
+        else if (d == 64) QT_LAUNCH_WS(64, true, true);
+        else if (d < 64) QT_LAUNCH_WS(64, false, true);
+        else QT_LAUNCH_WS(128, false, true);
+    } else if (d == 128) QT_LAUNCH_WS(128, true, false);
+    else if (d == 64) QT_LAUNCH_WS(64, true, false);
+    else if (d < 64) QT_LAUNCH_WS(64, false, false);
+    else QT_LAUNCH_WS(128, false, false);
 #undef QT_LAUNCH_WS
     QT_CHECK_LAUNCH("attention_decode_ws");
     if (n_splits > 1 && !cluster) {
@@ -143,18 +150,28 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
 extern "C" int qt_attention_prefill_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                         const int* block_table, int max_blocks, const int* seq_start, const int* seq_past,
                                         int n_seqs, int max_q_len, int nq, int nkv, int d, int page_tokens, int ring_tokens,
-                                        int window, float scale, void* stream) {
+                                        int window, float scale, const float* r1, const float* r2, void* stream) {
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
     int rc = check("attention_prefill_mma", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
     if (rc) return rc;
+    QT_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_prefill_mma: the distance penalty needs both of its factors");
+    QT_REQUIRE(r1 == nullptr || scale > 0.f, "attention_prefill_mma: with a distance penalty the score scale must be positive");
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, seq_start, seq_past, nullptr, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                1, nullptr, nullptr, 2};
+                1, nullptr, nullptr, 2, 0, r1, r2};
     const int lds = d + PAD;
     const size_t smem = (size_t)4 * PAGE * lds * 2;
     dim3 grid((max_q_len + PF_BQ - 1) / PF_BQ, nq, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-    if (d <= 64) {
+    if (r1 && d <= 64) {
+        static bool ok = false;
+        if (!ok) { rc = raise_smem(attention_prefill_mma_kernel<64, true>, 100 * 1024, "attention_prefill_mma"); if (rc) return rc; ok = true; }
+        launch_kernel(attention_prefill_mma_kernel<64, true>, dim3(grid), dim3(128), smem, s, p);
+    } else if (r1) {
+        static bool ok = false;
+        if (!ok) { rc = raise_smem(attention_prefill_mma_kernel<128, true>, 100 * 1024, "attention_prefill_mma"); if (rc) return rc; ok = true; }
+        launch_kernel(attention_prefill_mma_kernel<128, true>, dim3(grid), dim3(128), smem, s, p);
+    } else if (d <= 64) {
         static bool ok = false;
         if (!ok) { rc = raise_smem(attention_prefill_mma_kernel<64>, 100 * 1024, "attention_prefill_mma"); if (rc) return rc; ok = true; }
         launch_kernel(attention_prefill_mma_kernel<64>, dim3(grid), dim3(128), smem, s, p);

@@ -43,7 +43,17 @@ struct MmaParams {
     int n_splits; float* part_acc; float* part_ml;
     int stages;                    // decode: tiles in the shared-memory ring
     int cluster_merge;             // decode, one range per warp: the blocks of a (sequence, kv head) are a cluster and merge in shared memory
+    // Distance penalty (kernels instantiated with PEN): the score of key j for the query at position i loses
+    // r1[h] * ln(1 + r2[h] * (i - j)), one pair of factors per query head.  In the base-2 domain the kernels work in,
+    // that is r1 * log2(1 + r2 * distance) off the exponent; it is taken off the unscaled score as
+    // (r1 / (scale * log2 e)) * log2(1 + r2 * distance) before the row maximum, so the scale must be positive.
+    const float* r1 = nullptr;
+    const float* r2 = nullptr;
 };
+
+__device__ __forceinline__ float penalty_log2(float coefficient, float r2, int distance) {
+    return coefficient * __log2f(fmaf(r2, (float)distance, 1.f));
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -355,7 +365,7 @@ struct WarpTileCopy {
     }
 };
 
-template <int DMAX, bool EXACT>
+template <int DMAX, bool EXACT, bool PEN = false>
 __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(const MmaParams p) {
     pdl_launch_dependents();
     const bool merges_in_cluster = p.cluster_merge && gridDim.x > 1;
@@ -427,6 +437,12 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
 #pragma unroll
     for (int i = 0; i < DMAX / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     const float scale2 = p.scale * LOG2E;                            // positive (checked by the host)
+    float pen_c[2] = {0.f, 0.f}, pen_r2[2] = {0.f, 0.f};             // of this thread's two rows (query heads g and g + 8)
+    if (PEN) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+            if (g + 8 * r < rows) { pen_c[r] = p.r1[head_base + g + 8 * r] / scale2; pen_r2[r] = p.r2[head_base + g + 8 * r]; }
+    }
     const int mi = lane >> 3;
     const uint32_t k_lane = (uint32_t)(((mi >> 1) * 8 + (lane & 7)) * lds + (mi & 1) * 8) * 2u;
     const uint32_t v_lane = (uint32_t)(((mi & 1) * 8 + (lane & 7)) * lds + (mi >> 1) * 8) * 2u;
@@ -450,6 +466,13 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
                 mma_bf16(s[2], qf[ks], b1[0], b1[1]);
                 mma_bf16(s[3], qf[ks], b1[2], b1[3]);
             }
+        }
+        if (PEN) {                                                   // entries beyond the sequence are overwritten below
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    s[nt][e] -= penalty_log2(pen_c[e >> 1], pen_r2[e >> 1], len - 1 - (pos0 + nt * 8 + 2 * t + (e & 1)));
         }
         if (pos0 < lo || pos0 + WS_TILE > len) {                     // a tile at an edge of what the query sees
 #pragma unroll
@@ -599,7 +622,7 @@ __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc,
 // ----------------------------------------------------------------------------- prefill
 constexpr int PF_BQ = 64;
 
-template <int DMAX>
+template <int DMAX, bool PEN = false>
 __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const MmaParams p) {
     pdl_launch_dependents();
     pdl_wait();
@@ -652,6 +675,7 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
 #pragma unroll
     for (int i = 0; i < DMAX / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     const float scale2 = p.scale * LOG2E;
+    const float pen_c = PEN ? p.r1[head] / scale2 : 0.f, pen_r2 = PEN ? p.r2[head] : 0.f;
     // absolute positions of this thread's two query rows; rows beyond the sequence act as its last row
     const int qpos[2] = {min(past + q0 + warp * 16 + g, p_last), min(past + q0 + warp * 16 + g + 8, p_last)};
     const int warp_pos_min = min(past + q0 + warp * 16, p_last), warp_pos_max = min(past + q0 + warp * 16 + 15, p_last);
@@ -687,6 +711,13 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
             // and one ex2 per score.  Most tiles lie wholly below the diagonal (and inside the window) for every row
             // of the warp and need no mask.
             const bool all_visible = pos0 + PAGE - 1 <= warp_pos_min && (p.window <= 0 || pos0 > warp_pos_max - p.window);
+            if (PEN) {                                               // keys ahead of a row's query are overwritten by the mask below
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        s[nt][e] -= penalty_log2(pen_c, pen_r2, qpos[e >> 1] - (pos0 + nt * 8 + 2 * t + (e & 1)));
+            }
             float mx[2] = {-INFINITY, -INFINITY};
             if (!all_visible) {
 #pragma unroll

@@ -36,8 +36,52 @@ __device__ __forceinline__ int expert_of(const ExpertParams& p, int t, int k) {
     return e < 0 ? 0 : (e >= p.experts ? p.experts - 1 : e);          // never read outside the weights
 }
 
+// Eight consecutive elements of a weight row as floats, by 16-byte loads (rows that start on 16-byte boundaries).
+__device__ __forceinline__ void load8(const float* src, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(src)[0], b = reinterpret_cast<const float4*>(src)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* src, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { v[2 * j] = __low2float(h[j]); v[2 * j + 1] = __high2float(h[j]); }
+}
+
+// EV_FEATS dot products of consecutive weight rows (`stride` apart, `n` elements each) with a vector in shared memory,
+// summed over the warp.  VEC: n is a multiple of 8 and the rows start on 16-byte boundaries; every lane then loads 16
+// bytes of each row per turn, all rows' loads of a turn ahead of its arithmetic.
+template <typename T, bool VEC>
+__device__ __forceinline__ void warp_dots(const T* __restrict__ w, size_t stride, int rows, int n, const float* __restrict__ xs, int lane,
+                                          float (&acc)[EV_FEATS]) {
+#pragma unroll
+    for (int j = 0; j < EV_FEATS; ++j) acc[j] = 0.f;
+    if (VEC) {
+        for (int i = lane * 8; i < n; i += 256) {
+            float wv[EV_FEATS][8];
+#pragma unroll
+            for (int j = 0; j < EV_FEATS; ++j) load8(w + (size_t)(j < rows ? j : 0) * stride + i, wv[j]);
+            const float4 xa = *reinterpret_cast<const float4*>(xs + i), xb = *reinterpret_cast<const float4*>(xs + i + 4);
+            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int j = 0; j < EV_FEATS; ++j)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[j] += wv[j][e] * xv[e];
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+            const float xv = xs[i];
+#pragma unroll
+            for (int j = 0; j < EV_FEATS; ++j)
+                if (j < rows) acc[j] += to_float(w[(size_t)j * stride + i]) * xv;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < EV_FEATS; ++j) acc[j] = warp_sum(acc[j]);
+}
+
 // mid[pair, f] = act(W_up[e][f, :] . x[t, :]).  grid (pairs, feature blocks); x[t] in shared memory as float.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(EV_WARPS * 32) expert_up_kernel(const ExpertParams p) {
     pdl_launch_dependents();
     pdl_wait();
@@ -51,24 +95,16 @@ __global__ void __launch_bounds__(EV_WARPS * 32) expert_up_kernel(const ExpertPa
     const T* w = (const T*)p.up + (size_t)e * p.ff * p.width;
     T* mid = (T*)p.mid + (size_t)pair * p.ff;
     const int f0 = (blockIdx.y * EV_WARPS + warp) * EV_FEATS;
+    if (f0 >= p.ff) return;
     float acc[EV_FEATS];
+    warp_dots<T, VEC>(w + (size_t)f0 * p.width, (size_t)p.width, p.ff - f0, p.width, xs, lane, acc);
 #pragma unroll
-    for (int j = 0; j < EV_FEATS; ++j) acc[j] = 0.f;
-    for (int i = lane; i < p.width; i += 32) {
-        const float xv = xs[i];
-#pragma unroll
-        for (int j = 0; j < EV_FEATS; ++j)
-            if (f0 + j < p.ff) acc[j] += to_float(w[(size_t)(f0 + j) * p.width + i]) * xv;
-    }
-#pragma unroll
-    for (int j = 0; j < EV_FEATS; ++j) {
-        const float total = warp_sum(acc[j]);
-        if (lane == 0 && f0 + j < p.ff) mid[f0 + j] = from_float<T>(gate_activation<false>(total, p.act));
-    }
+    for (int j = 0; j < EV_FEATS; ++j)
+        if (lane == 0 && f0 + j < p.ff) mid[f0 + j] = from_float<T>(gate_activation<false>(acc[j], p.act));
 }
 
 // out[t, c] = pair_weight * sum_k W_down[e_k][c, :] . mid[t * top + k, :].  grid (tokens, column blocks).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(EV_WARPS * 32) expert_down_kernel(const ExpertParams p) {
     pdl_launch_dependents();
     pdl_wait();
@@ -79,25 +115,21 @@ __global__ void __launch_bounds__(EV_WARPS * 32) expert_down_kernel(const Expert
     for (int i = threadIdx.x; i < p.top * p.ff; i += blockDim.x) ms[i] = to_float(mid[i]);
     __syncthreads();
     const int c0 = (blockIdx.y * EV_WARPS + warp) * EV_FEATS;
-    float acc[EV_FEATS];
+    if (c0 >= p.width) return;
+    float total[EV_FEATS];
 #pragma unroll
-    for (int j = 0; j < EV_FEATS; ++j) acc[j] = 0.f;
-    for (int k = 0; k < p.top; ++k) {
+    for (int j = 0; j < EV_FEATS; ++j) total[j] = 0.f;
+    for (int k = 0; k < p.top; ++k) {                      // in the order of the table's row
         const int e = expert_of(p, t, k);
         const T* w = (const T*)p.down + (size_t)e * p.width * p.ff;
-        const float* m = ms + k * p.ff;
-        for (int i = lane; i < p.ff; i += 32) {
-            const float mv = m[i];
+        float acc[EV_FEATS];
+        warp_dots<T, VEC>(w + (size_t)c0 * p.ff, (size_t)p.ff, p.width - c0, p.ff, ms + k * p.ff, lane, acc);
 #pragma unroll
-            for (int j = 0; j < EV_FEATS; ++j)
-                if (c0 + j < p.width) acc[j] += to_float(w[(size_t)(c0 + j) * p.ff + i]) * mv;
-        }
+        for (int j = 0; j < EV_FEATS; ++j) total[j] += acc[j];
     }
 #pragma unroll
-    for (int j = 0; j < EV_FEATS; ++j) {
-        const float total = warp_sum(acc[j]);
-        if (lane == 0 && c0 + j < p.width) p.out[(size_t)t * p.width + c0 + j] = total * p.pair_weight;
-    }
+    for (int j = 0; j < EV_FEATS; ++j)
+        if (lane == 0 && c0 + j < p.width) p.out[(size_t)t * p.width + c0 + j] = total[j] * p.pair_weight;
 }
 
 static int check_experts(const char* name, int n_tokens, int vocab, int top, int experts, int width, int ff, int act) {
@@ -119,11 +151,22 @@ extern "C" int qt_experts_by_pair(const void* x, const int* token_ids, const int
     const int per_block = EV_WARPS * EV_FEATS;
     return QT_DISPATCH_DTYPE(dtype, "experts_by_pair", {
         const size_t smem_up = (size_t)width * sizeof(float), smem_down = (size_t)top * ff * sizeof(float);
-        if (smem_up > 48 * 1024) cudaFuncSetAttribute(expert_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
-        if (smem_down > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
-        launch_kernel(expert_up_kernel<T>, dim3(n_tokens * top, (ff + per_block - 1) / per_block), dim3(EV_WARPS * 32), smem_up, s, p);
-        QT_CHECK_LAUNCH("expert_up");
-        launch_kernel(expert_down_kernel<T>, dim3(n_tokens, (width + per_block - 1) / per_block), dim3(EV_WARPS * 32), smem_down, s, p);
+        const dim3 grid_up(n_tokens * top, (ff + per_block - 1) / per_block), grid_down(n_tokens, (width + per_block - 1) / per_block);
+        // 16-byte loads: rows of both weights, and the experts' matrices, start on 16-byte boundaries
+        const bool vec = width % 8 == 0 && ff % 8 == 0 && (uintptr_t)up % 16 == 0 && (uintptr_t)down % 16 == 0;
+        if (vec) {
+            if (smem_up > 48 * 1024) cudaFuncSetAttribute(expert_up_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
+            if (smem_down > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+            launch_kernel(expert_up_kernel<T, true>, grid_up, dim3(EV_WARPS * 32), smem_up, s, p);
+            QT_CHECK_LAUNCH("expert_up");
+            launch_kernel(expert_down_kernel<T, true>, grid_down, dim3(EV_WARPS * 32), smem_down, s, p);
+        } else {
+            if (smem_up > 48 * 1024) cudaFuncSetAttribute(expert_up_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
+            if (smem_down > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+            launch_kernel(expert_up_kernel<T, false>, grid_up, dim3(EV_WARPS * 32), smem_up, s, p);
+            QT_CHECK_LAUNCH("expert_up");
+            launch_kernel(expert_down_kernel<T, false>, grid_down, dim3(EV_WARPS * 32), smem_down, s, p);
+        }
         QT_CHECK_LAUNCH("expert_down");
         return QT_OK;
     });

@@ -54,9 +54,9 @@ _SIGNATURES = {
         "qt_attention_decode_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
         "qt_attention_decode_ws": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
-                                   _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
+                                   _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
         "qt_attention_prefill_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
-                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr],
     },
     "attention_tc": {
         "qt_attention_prefill_tc": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
@@ -378,8 +378,22 @@ def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_t
 
 
 def _plain_attention(q: torch.Tensor, v_cache: torch.Tensor, penalty) -> bool:
-    """Whether the tensor-core attention kernels may take this call: values as wide as keys, no distance penalty."""
+    """Whether every tensor-core attention kernel may take this call: values as wide as keys, no distance penalty."""
     return penalty is None and v_cache.shape[-1] == q.shape[2]
+
+
+def _penalised_choice(q: torch.Tensor, v_cache: torch.Tensor, page_tokens: int, scale: float, impl: str | None, mma: str) -> str:
+    """The kernel for a call that is not plain: the mma.sync kernels compute the distance penalty (values as wide as
+    keys, a positive scale); the generic kernels take the rest."""
+    fits = v_cache.shape[-1] == q.shape[2] and attention_mma_supported(q, page_tokens) and scale > 0
+    if impl in (None, mma):
+        if fits:
+            return mma
+        if impl is None:
+            return "generic"
+    if impl != "generic":
+        raise KernelError(f"attention kernel {impl!r} does not take this call (a distance penalty, or values of another head size)")
+    return "generic"
 
 
 def attention_mma_supported(q: torch.Tensor, page_tokens: int) -> bool:
@@ -416,9 +430,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     r1_h * ln(1 + r2_h * (i - j))."""
     _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
     if not _plain_attention(q, v_cache, penalty):
-        if impl not in (None, "generic"):
-            raise KernelError(f"attention kernel {impl!r} takes neither a distance penalty nor values of another head size")
-        impl = "generic"
+        impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "mma")
     n_seqs = seq_past.shape[0]
     _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
     _need(seq_past, "seq_past", torch.int32)
@@ -434,7 +446,8 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     if choice == "mma":
         _call("attention_mma", "qt_attention_prefill_mma", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out),
               _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
-              num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), _stream())
+              num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale),
+              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, _stream())
         return
     _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
@@ -470,9 +483,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
     if not _plain_attention(q, v_cache, penalty):
-        if impl not in (None, "generic"):
-            raise KernelError(f"attention kernel {impl!r} takes neither a distance penalty nor values of another head size")
-        impl = "generic"
+        impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "ws")
     if n_splits > 1:
         _need(part_acc, "part_acc", torch.float32)
         _need(part_ml, "part_ml", torch.float32)
@@ -489,7 +500,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     if picked == "ws" and _ws_merges_in_cluster(n_splits, warps, num_heads // num_kv_heads, head_dim):
         launches = 1
     if picked == "ws":
-        _call("attention_mma", "qt_attention_decode_ws", *common, int(warps), _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
+        _call("attention_mma", "qt_attention_decode_ws", *common, int(warps), _ptr(part_acc), _ptr(part_ml),
+              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, _stream(), launches=launches)
     elif picked == "mma":
         _call("attention_mma", "qt_attention_decode_mma", *common, _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
     else:

@@ -78,8 +78,9 @@ class Attention:
         self.treated = self.v_norm_eps is not None or self.v_blend is not None or self.dv != self.d
         if self.treated and (self.qk_norm or not self.own_kv or position_spec.kind != "none"):
             raise ValueError(f"{prefix}: treated values (v_norm, v_blend, v_head_dim) go with no rotation, no q/k norm and keys of the layer's own")
-        # the tensor-core attention kernels take neither a distance penalty nor values of another head size
-        self.plain_scores = not self.penalised and self.dv == self.d
+        # the mma.sync attention kernels take values as wide as the keys (and compute the distance penalty, given a
+        # positive scale); everything else goes to the generic kernels
+        self.mma_scores = self.dv == self.d and (not self.penalised or self.scale > 0)
         proj_rows = self.nq * self.d + (self.nkv * (self.d + self.dv) if self.own_kv else 0)
         if self.treated:
             self.qkv = Linear("attn.qkv.sums", proj_rows, self.hidden, runtime, float_out=True)      # float sums: the bias is added behind it
@@ -190,7 +191,7 @@ class Attention:
         span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
         group = self.nq // self.nkv
         most = max(1, min(_MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
-        if self.plain_scores and self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128 and cache.page_tokens == 64:
+        if self.mma_scores and self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128 and cache.page_tokens == 64:
             pairs = ctx.n_seqs * self.nkv * math.ceil(group / 16)
             tiles = math.ceil(span / 32)
             sms = self.runtime.sm_count

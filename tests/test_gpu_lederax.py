@@ -143,7 +143,8 @@ def paged(values: torch.Tensor, page_tokens: int, order: list[int], dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, kv_heads, d, dv, window", [(4, 2, 16, 32, 21), (3, 3, 40, 8, None), (8, 1, 64, 64, 64), (2, 1, 24, 130, 1)])
+@pytest.mark.parametrize("heads, kv_heads, d, dv, window", [(4, 2, 16, 32, 21), (3, 3, 40, 8, None), (8, 1, 64, 64, 64), (2, 1, 24, 130, 1),
+                                                             (6, 2, 32, 32, 50), (2, 1, 128, 128, None), (34, 2, 48, 48, 129)])
 def test_attention_with_distance_penalty_and_window_edges(dtype, heads, kv_heads, d, dv, window):
     """Prompt portions and one-token steps over a scrambled paged cache.  The keys just inside and just outside the
     window of the last queries, and one far key, are made to match their queries (score far above the rest): a window
