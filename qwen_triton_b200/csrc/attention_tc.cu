@@ -27,6 +27,11 @@
 // absolute position p iff j <= p and, in a windowed group, j > p - window.  Every mbarrier wait is bounded and
 // reports through a status word.
 //
+// PEN: a distance penalty, the score of key j for the query at position i loses r1_h ln(1 + r2_h (i - j)).  The softmax
+// thread takes it off the row it holds in registers before the maximum, in the base-2 domain the row is scaled into:
+// s - (r1 / (scale log2 e)) log2(1 + r2 (i - j)), one FMA for the argument (the key's place in the tile is a constant
+// of the unrolled loop), lg2.approx, one FMA; keys ahead of the query give arguments that the mask then overwrites.
+//
 // Counterpart in luozoupi/Qwen-Triton: kernels/flash_attention.py:54-152 (32 x 32 tl.dot tiles) and the masked
 // SDPA branch of modules/attention.py:110-123.
 #include "tc_common.cuh"
@@ -54,7 +59,15 @@ struct TcAttnParams {
     int nq, nkv, ring_tokens, window;
     float scale;
     int* status;
+    const float* r1;               // [nq] factors of the distance penalty (PEN), else null
+    const float* r2;
 };
+
+__device__ __forceinline__ float fast_log2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -128,7 +141,7 @@ __device__ __forceinline__ int cache_page(const int* table, int max_blocks, int 
 
 // BKEY: keys per tile, one page or two.  One page: half the shared memory and tensor memory, so that two blocks share
 // an SM and one's softmax runs under the other's MMAs.
-template <int HD, int BKEY>
+template <int HD, int BKEY, bool PEN>
 __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                        const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v,
@@ -281,6 +294,7 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int qpos = min(past + q0 + r, p_last);       // rows beyond the sequence act as its last row
         const float scale2 = p.scale * LOG2E;
+        const float pen_c = PEN ? -p.r1[head] / scale2 : 0.f, pen_r2 = PEN ? -p.r2[head] : 0.f;     // negated once, for the FMAs
         float m_run = -INFINITY, l_run = 0.f;              // the maximum this row scales by (scaled base-2 domain) and its sum
         pdl_wait();                                        // the output may still be read by an earlier kernel
         bool ok = true;
@@ -296,6 +310,14 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
 #pragma unroll
             for (int q = 0; q < QUARTERS; ++q) tmem_load32_start(s_addr + (uint32_t)(q * 32), v[q]);
             tmem_wait_ld();
+            if (PEN) {
+                const float first = fmaf(-pen_r2, (float)(qpos - pos0), 1.f);      // 1 + r2 * distance to the tile's first key
+#pragma unroll
+                for (int q = 0; q < QUARTERS; ++q)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        v[q][c] = __float_as_uint(fmaf(pen_c, fast_log2(fmaf(pen_r2, (float)(q * 32 + c), first)), __uint_as_float(v[q][c])));
+            }
             // mask only where some row of the block cannot see the whole tile
             const bool masked = pos0 + BKEY - 1 > p_first || (p.window > 0 && pos0 <= p_last - p.window);
             if (masked) {
@@ -399,7 +421,7 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
     }
 }
 
-template <int HD, int BKEY>
+template <int HD, int BKEY, bool PEN>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const TcAttnParams& p, int n_seqs,
            int max_q_len, cudaStream_t stream) {
     constexpr uint32_t HALVES = HD / 64;
@@ -407,12 +429,12 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap
     const size_t smem = (size_t)HALVES * HALF_BYTES + 4 * (size_t)HALVES * BKEY * 128 + ALIGN_SLACK + 128 + 64;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, BKEY>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, BKEY, PEN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "attention_prefill_tc: cannot raise shared memory: %s", cudaGetErrorString(err));
         configured = true;
     }
     dim3 grid(p.nq, (max_q_len + BQ - 1) / BQ, n_seqs);
-    launch_kernel(attention_prefill_tc_kernel<HD, BKEY>, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p);
+    launch_kernel(attention_prefill_tc_kernel<HD, BKEY, PEN>, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p);
     QT_CHECK_LAUNCH("attention_prefill_tc");
     return QT_OK;
 }
@@ -424,7 +446,8 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap
 extern "C" int qt_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
                                        int n_pages, const int* block_table, int max_blocks, const int* seq_start,
                                        const int* seq_past, int n_seqs, int max_q_len, int nq, int nkv, int d,
-                                       int page_tokens, int ring_tokens, int window, float scale, int* status, void* stream) {
+                                       int page_tokens, int ring_tokens, int window, float scale, const float* r1, const float* r2,
+                                       int* status, void* stream) {
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
     QT_REQUIRE(n_seqs > 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill_tc: bad head counts nq=%d nkv=%d (B=%d)", nq, nkv, n_seqs);
     QT_REQUIRE(d == 64 || d == 128, "attention_prefill_tc: head_dim=%d (this kernel takes 64 or 128)", d);
@@ -433,6 +456,8 @@ extern "C" int qt_attention_prefill_tc(const void* q, const void* k_cache, const
     QT_REQUIRE(ring_tokens == 0 || (window > 0 && ring_tokens >= window), "attention_prefill_tc: a ring of %d tokens cannot hold a window of %d", ring_tokens, window);
     QT_REQUIRE(n_seqs <= 65535 && (max_q_len + BQ - 1) / BQ <= 65535 && max_blocks > 0 && n_pages > 0 && n_tokens > 0, "attention_prefill_tc: bad sizes");
     QT_REQUIRE(status != nullptr, "attention_prefill_tc: a status word is required");
+    QT_REQUIRE((r1 == nullptr) == (r2 == nullptr) && (r1 == nullptr || scale > 0.f),
+               "attention_prefill_tc: the distance penalty needs both of its factors and a positive score scale");
     QT_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)out % 16 == 0),
                "attention_prefill_tc: operands must be 16-byte aligned");
     CUtensorMap map_q, map_k, map_v;
@@ -442,11 +467,15 @@ extern "C" int qt_attention_prefill_tc(const void* q, const void* k_cache, const
     if (rc) return rc;
     rc = tensor_map(&map_v, v_cache, (uint64_t)n_pages * nkv * PAGE, (uint64_t)d, PAGE);
     if (rc) return rc;
-    TcAttnParams p{(__nv_bfloat16*)out, block_table, max_blocks, seq_start, seq_past, nq, nkv, ring_tokens, window, scale, status};
+    TcAttnParams p{(__nv_bfloat16*)out, block_table, max_blocks, seq_start, seq_past, nq, nkv, ring_tokens, window, scale, status, r1, r2};
     cudaStream_t s = (cudaStream_t)stream;
     // key tiles of one page, two blocks per SM: measured 12-22 % faster than tiles of two pages with one block per SM
-    if (d == 64) return launch<64, 64>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
-    return launch<128, 64>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
+    if (r1) {
+        if (d == 64) return launch<64, 64, true>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
+        return launch<128, 64, true>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
+    }
+    if (d == 64) return launch<64, 64, false>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
+    return launch<128, 64, false>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
 }
 
 QT_DEFINE_LAST_ERROR(attention_tc)

@@ -6,8 +6,11 @@
 // [E * N, K]; a weight tile of 128 rows that reaches past its expert's N rows reads the next expert's (or zeros past
 // the end), and the epilogue drops those columns.
 //
-// The rows are the MMA's M (128 per block), the weight rows its N (128): a thread of the epilogue holds 32 consecutive
-// output features of one row per tcgen05.ld, applies the activation where asked and stores 16 bytes at a time.
+// The rows are the MMA's M (128 per block), the weight rows its N (256 where there are tiles for several waves, else 128): a thread
+// of the epilogue holds 32 consecutive output features of one row per tcgen05.ld, applies the activation where asked
+// and stores 16 bytes at a time.  Two blocks share an SM (96 KB of shared memory and at most 256 columns of tensor
+// memory each) at N = 128 with a three-stage ring, so one's epilogue runs under the other's MMAs; at N = 256 a block has
+// the SM to itself and a four-stage ring.
 // TMA (128-byte swizzle) stages 64-element K slices in a ring; one elected thread issues tcgen05.mma, the
 // accumulator lives in tensor memory.  Warp roles and the bounded waits are those of gemm_tc.cu.
 #include "tc_common.cuh"
@@ -18,12 +21,10 @@ using namespace qt_tc;
 namespace {
 
 constexpr int BM = 128;        // rows per tile = MMA M
-constexpr int BN = 128;        // weight rows per tile = MMA N
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 3;      // 96 KB: two blocks share an SM, one's epilogue runs under the other's MMAs
+constexpr uint32_t A_BYTES = BM * BK * 2;
 
 __device__ __forceinline__ void store8(float* dst, const float (&f)[8]) {
     reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
@@ -39,12 +40,13 @@ __device__ __forceinline__ void store8(__nv_bfloat16* dst, const float (&f)[8]) 
     *reinterpret_cast<uint4*>(dst) = packed;
 }
 
-template <typename TO, bool ACT>
+template <typename TO, bool ACT, int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS) expert_gemm_kernel(const __grid_constant__ CUtensorMap map_x,
                                                               const __grid_constant__ CUtensorMap map_w, TO* __restrict__ out,
                                                               const int* __restrict__ tile_expert, int n_out, int kb_total,
                                                               int w_tiles, int act, int* status) {
-    // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N = 128, M = 128
+    constexpr uint32_t B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N = BN, M = 128
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     pdl_launch_dependents();
@@ -146,21 +148,39 @@ __global__ void __launch_bounds__(THREADS) expert_gemm_kernel(const __grid_const
     }
 }
 
-template <typename TO, bool ACT>
-int launch(const CUtensorMap& map_x, const CUtensorMap& map_w, TO* out, const int* tile_expert, int max_tiles, int n_out, int kb_total,
-           int act, int* status, cudaStream_t stream) {
-    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
+template <typename TO, bool ACT, int BN, int STAGES>
+int launch_tile(const void* x, const void* w, TO* out, const int* tile_expert, int max_tiles, int experts, int n_out, int K, int act, int* status,
+                cudaStream_t stream) {
+    CUtensorMap map_x, map_w;
+    int rc = tensor_map(&map_x, x, (uint64_t)max_tiles * BM, (uint64_t)K, BM);
+    if (rc) return rc;
+    rc = tensor_map(&map_w, w, (uint64_t)experts * n_out, (uint64_t)K, BN);
+    if (rc) return rc;
+    const size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024 + (2 * STAGES + 1) * 8 + 16;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(expert_gemm_kernel<TO, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(expert_gemm_kernel<TO, ACT, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "expert_gemm: cannot raise shared memory: %s", cudaGetErrorString(err));
         configured = true;
     }
-    const int w_tiles = (n_out + BN - 1) / BN;
-    launch_kernel(expert_gemm_kernel<TO, ACT>, dim3((unsigned)(max_tiles * w_tiles)), dim3(THREADS), smem, stream, map_x, map_w, out, tile_expert,
-                  n_out, kb_total, w_tiles, act, status);
+    const int w_tiles = (n_out + BN - 1) / BN, kb_total = (K + BK - 1) / BK;
+    QT_REQUIRE((long long)max_tiles * w_tiles < (1ll << 31), "expert_gemm: too many tiles for one launch");
+    launch_kernel(expert_gemm_kernel<TO, ACT, BN, STAGES>, dim3((unsigned)(max_tiles * w_tiles)), dim3(THREADS), smem, stream, map_x, map_w, out,
+                  tile_expert, n_out, kb_total, w_tiles, act, status);
     QT_CHECK_LAUNCH("expert_gemm");
     return QT_OK;
+}
+
+template <typename TO, bool ACT>
+int launch(const void* x, const void* w, TO* out, const int* tile_expert, int max_tiles, int experts, int n_out, int K, int act, int* status,
+           cudaStream_t stream) {
+    // 128 x 256 tiles (one block per SM, four-stage ring) fetch a third less per flop than 128 x 128 ones and run at
+    // 900-1,050 TFLOP/s where there are tiles for several waves (8,192 tokens, 16 experts of 4,096 x 2,048); with few
+    // tiles the smaller ones, two blocks to an SM, fill the last wave better (2,048 tokens: 114 against 132 us).
+    const long long wide_items = (long long)max_tiles * ((n_out + 255) / 256);
+    if (n_out > 128 && wide_items >= 4ll * sm_count())
+        return launch_tile<TO, ACT, 256, 4>(x, w, out, tile_expert, max_tiles, experts, n_out, K, act, status, stream);
+    return launch_tile<TO, ACT, 128, 3>(x, w, out, tile_expert, max_tiles, experts, n_out, K, act, status, stream);
 }
 
 }  // namespace
@@ -174,17 +194,10 @@ extern "C" int qt_expert_gemm(const void* x, const void* w, void* out, int out_d
     QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0), "expert_gemm: operands must be 16-byte aligned");
     QT_REQUIRE(act < QT_ACT_COUNT, "expert_gemm: unknown activation code %d", act);
     QT_REQUIRE(status != nullptr && tile_expert != nullptr, "expert_gemm: a status word and the tiles' experts are required");
-    QT_REQUIRE((long long)max_tiles * ((n_out + BN - 1) / BN) < (1ll << 31), "expert_gemm: too many tiles for one launch");
-    CUtensorMap map_x, map_w;
-    int rc = tensor_map(&map_x, x, (uint64_t)max_tiles * BM, (uint64_t)K, BM);
-    if (rc) return rc;
-    rc = tensor_map(&map_w, w, (uint64_t)experts * n_out, (uint64_t)K, BN);
-    if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    const int kb_total = (K + BK - 1) / BK;
-    if (out_dtype == QT_BF16 && act >= 0) return launch<__nv_bfloat16, true>(map_x, map_w, (__nv_bfloat16*)out, tile_expert, max_tiles, n_out, kb_total, act, status, s);
-    if (out_dtype == QT_BF16) return launch<__nv_bfloat16, false>(map_x, map_w, (__nv_bfloat16*)out, tile_expert, max_tiles, n_out, kb_total, 0, status, s);
-    if (out_dtype == QT_F32 && act < 0) return launch<float, false>(map_x, map_w, (float*)out, tile_expert, max_tiles, n_out, kb_total, 0, status, s);
+    if (out_dtype == QT_BF16 && act >= 0) return launch<__nv_bfloat16, true>(x, w, (__nv_bfloat16*)out, tile_expert, max_tiles, experts, n_out, K, act, status, s);
+    if (out_dtype == QT_BF16) return launch<__nv_bfloat16, false>(x, w, (__nv_bfloat16*)out, tile_expert, max_tiles, experts, n_out, K, 0, status, s);
+    if (out_dtype == QT_F32 && act < 0) return launch<float, false>(x, w, (float*)out, tile_expert, max_tiles, experts, n_out, K, 0, status, s);
     QT_FAIL(QT_ERR_ARG, "expert_gemm: output type %d%s is not offered", out_dtype, act >= 0 ? " with an activation" : "");
 }
 

@@ -60,7 +60,7 @@ _SIGNATURES = {
     },
     "attention_tc": {
         "qt_attention_prefill_tc": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
-                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr],
+                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     },
     "gemm_simt": {
         "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
@@ -383,9 +383,12 @@ def _plain_attention(q: torch.Tensor, v_cache: torch.Tensor, penalty) -> bool:
 
 
 def _penalised_choice(q: torch.Tensor, v_cache: torch.Tensor, page_tokens: int, scale: float, impl: str | None, mma: str) -> str:
-    """The kernel for a call that is not plain: the mma.sync kernels compute the distance penalty (values as wide as
-    keys, a positive scale); the generic kernels take the rest."""
+    """The kernel for a call that is not plain: the tensor-core kernels compute the distance penalty (values as wide
+    as keys, a positive scale; ``mma`` names the mma.sync kernel of the caller, and a prefill of head size 64 or 128
+    takes the tcgen05 kernel first); the generic kernels take the rest."""
     fits = v_cache.shape[-1] == q.shape[2] and attention_mma_supported(q, page_tokens) and scale > 0
+    if fits and mma == "mma" and impl in (None, "tc") and attention_tc_supported(q, page_tokens):
+        return "tc"
     if impl in (None, mma):
         if fits:
             return mma
@@ -441,6 +444,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _call("attention_tc", "qt_attention_prefill_tc", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), q.shape[0],
               k_cache.shape[0], _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs,
               int(max_q_len), num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale),
+              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None,
               _ptr(_status_word(q.device)), _stream())
         return
     if choice == "mma":

@@ -232,13 +232,14 @@ def test_values_are_normed_blended_and_cached(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tokens, experts, top, width, ff", [(5, 3, 1, 40, 24), (33, 4, 4, 64, 72), (300, 12, 2, 128, 96), (700, 5, 3, 72, 200)])
+@pytest.mark.parametrize("tokens, experts, top, width, ff", [(5, 3, 1, 40, 24), (33, 4, 4, 64, 72), (300, 12, 2, 128, 96), (700, 5, 3, 72, 200),
+                                                               (1500, 6, 2, 512, 320), (2048, 4, 2, 256, 4360)])
 def test_experts_chosen_by_the_token_table(dtype, tokens, experts, top, width, ff):
     torch.manual_seed(tokens)
     store = STORE[dtype]
     vocab = 50
-    up = (torch.randn(experts, ff, width) * 0.2).to(store)
-    down = (torch.randn(experts, width, ff) * 0.2).to(store)
+    up = (torch.randn(experts, ff, width) * width ** -0.5).to(store)          # results of the order of 1
+    down = (torch.randn(experts, width, ff) * 2.0 * ff ** -0.5).to(store)
     table = torch.stack([torch.randperm(experts)[:top] for _ in range(vocab)]).to(torch.int32)
     ids = torch.randint(0, vocab, (tokens,), dtype=torch.int32)
     x = torch.randn(tokens, width).to(store)
@@ -248,7 +249,7 @@ def test_experts_chosen_by_the_token_table(dtype, tokens, experts, top, width, f
     want = plain.routed_experts(x.float(), ids.long(), weights, "m", {"router": {"top": top}})
     from qwen_triton_b200.parts.base import Runtime, Workspace
     from qwen_triton_b200.parts.feed_forward import TableExperts
-    runtime = Runtime(device=torch.device(DEV), dtype=store, max_step_tokens=1024, max_positions=64, workspace=Workspace(torch.device(DEV)))
+    runtime = Runtime(device=torch.device(DEV), dtype=store, max_step_tokens=2048, max_positions=64, workspace=Workspace(torch.device(DEV)))
     part = TableExperts({"hidden_size": width, "expert_size": ff, "experts": experts, "top": top, "vocab_size": vocab,
                          "activation": "gelu", "expert": "e{}", "weight_suffix": ""}, "m", runtime)
     runtime.workspace.allocate()
@@ -383,3 +384,64 @@ def test_random_weights_on_the_device_equal_the_written_folder():
         a = run_whole(Engine.from_pretrained(folder, dtype="fp32", max_tokens=256), tokens)
     b = run_whole(Engine.from_config(config, seed=9, dtype="fp32", max_tokens=256), tokens)
     assert torch.equal(a, b)
+
+
+# ----------------------------------------------------------------------------- as a user runs it
+def test_command_line_with_a_preset_and_random_weights():
+    """``scripts.smoke`` as a child process: weights drawn on the device from --seed, prompts of random ids; the same
+    draw on the host gives the oracle its model."""
+    import ast
+    import re
+    import subprocess
+    import sys
+    from qwen_triton_b200.engine.model import expected_tensors
+    from qwen_triton_b200.weights import random_tensor
+    name, seed, lengths = "lederax-tiny-b", 4, (9, 30)
+    config = load_preset(name)
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run([sys.executable, "-m", "qwen_triton_b200.scripts.smoke", "--preset", name, "--random-weights", "--seed", str(seed),
+                           "--dtype", "fp32", "--random-prompts", ",".join(map(str, lengths)), "--max-new-tokens", "5", "--ignore-eos",
+                           "--max-tokens", "512"], cwd=root, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    got = [ast.literal_eval(m.group(1)) for m in re.finditer(r"generated=(\[.*?\]) finish=length", proc.stdout)]
+    weights = {n: random_tensor(n, spec, seed, torch.float32 if spec.role != "table" else torch.int32)
+               for n, spec in expected_tensors(config.model_spec()).items() if not spec.optional}
+    generator = torch.Generator().manual_seed(seed)
+    prompts = [torch.randint(0, config.vocab_size, (n,), generator=generator).tolist() for n in lengths]
+    assert got == [plain.greedy_generate(config.to_hf_dict(), weights, p, 5) for p in prompts]
+
+
+@pytest.mark.parametrize("dtype, name", [("float32", "fp32"), ("bfloat16", "bf16")])
+def test_trace_replay_of_a_folder(tmp_path, dtype, name):
+    """``bin/trace_run`` as a child process on a model folder of the design: a batch of unequal prompts, then their
+    next tokens one by one, one request ending early; under a --max-tokens of exactly what is live at most."""
+    import json
+    import subprocess
+    import sys
+    import numpy as np
+    model_name = "lederax-tiny-a"
+    folder = model(model_name, name)[0]
+    lengths = {"a": 70, "b": 3, "c": 129}
+    requests = {key: tokens_of(model_name, n + 4, 60 + n) for key, n in lengths.items()}
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": r[:lengths[k]], "want": [lengths[k] - 1]} for k, r in requests.items()], "end": []}]
+    for t in range(4):
+        live = [k for k in requests if not (k == "b" and t >= 2)]
+        steps.append({"step": t + 1, "entries": [{"id": k, "tokens": [requests[k][lengths[k] + t]], "want": [0] if t != 1 else []} for k in live],
+                      "end": (["b"] if t == 1 else []) + (live if t == 3 else [])})
+    most = 128 + 64 + 192                      # each request rounded up to whole pages of 64
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(tmp_path),
+                           "--max-tokens", str(most)], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    assert [line for line in proc.stdout.splitlines() if line.startswith("done ")] == [f"done {i}" for i in range(5)]
+    vocab = config_of(model_name).vocab_size
+    for step in steps:
+        wanted = [(e["id"], w) for e in step["entries"] for w in e["want"]]
+        path = tmp_path / f"{step['step']}.f32"
+        if not wanted:
+            assert not path.exists()
+            continue
+        got = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(len(wanted), vocab).copy())
+        for row, (key, _) in enumerate(wanted):
+            at = lengths[key] - 1 + step["step"]
+            close(got[row:row + 1], oracle(model_name, name, False, tuple(requests[key]))[at:at + 1], name, f"step {step['step']} request {key}")
