@@ -651,6 +651,74 @@ __global__ void qkv_treat_write_kernel(const QkvTreatParams p) {
     }
 }
 
+// The same for head sizes that are multiples of 4 up to 256 and 16-byte aligned rows: a lane owns up to two pieces of
+// four consecutive elements, sums the split-K partials with independent 16-byte loads and keeps the values in
+// registers between the sum of squares and the stores.
+template <typename TI, typename TO>
+__global__ void qkv_treat_write_vec_kernel(const QkvTreatParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = p.nq + 2 * p.nkv;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long long)p.n_tokens * heads_total) return;
+    const int t = (int)(item / heads_total);
+    const int head = (int)(item % heads_total);
+    const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
+    if (!is_q && !p.write_kv) return;
+    const int row_width = (p.nq + p.nkv) * p.d + p.nkv * p.dv;
+    const int col0 = is_q ? head * p.d : (is_k ? p.nq * p.d + (head - p.nq) * p.d : (p.nq + p.nkv) * p.d + (head - p.nq - p.nkv) * p.dv);
+    const int len = (is_q || is_k) ? p.d : p.dv;
+    const int chunks = len >> 2;
+    const TI* in = (const TI*)p.qkv + (size_t)t * row_width + col0;
+    float4 x[2];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) {
+            float4 v = load4(in + 4 * c);
+            add_splits4<16>(v, in + 4 * c, 1, p.n_splits, p.split_stride);
+            if (p.bias) { const float4 b = load4(p.bias + col0 + 4 * c); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+            x[i] = v;
+            sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    const int pos = p.token_pos[t];
+    TO* dst;
+    if (is_q) dst = (TO*)p.q_out + ((size_t)t * p.nq + head) * p.d;
+    else {
+        const int* table = p.block_table + (size_t)p.token_seq[t] * p.max_blocks;
+        dst = is_k ? (TO*)p.k_cache + cache_offset(table, pos, p.ring_tokens, p.page_tokens, p.nkv, head - p.nq, p.d)
+                   : (TO*)p.v_cache + cache_offset(table, pos, p.ring_tokens, p.page_tokens, p.nkv, head - p.nq - p.nkv, p.dv);
+    }
+    if (is_q || is_k) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int c = lane + 32 * i;
+            if (c < chunks) store4(dst + 4 * c, x[i]);
+        }
+        return;
+    }
+    const float inv = p.v_norm ? 1.f / sqrtf(warp_sum(sq) / (float)len + p.v_eps) : 1.f;
+    const float lambda = p.blend_from ? p.blend_lambda[0] : 0.f;
+    const size_t side = ((size_t)t * p.nkv + (head - p.nq - p.nkv)) * p.dv;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c = lane + 32 * i;
+        if (c < chunks) {
+            float4 v = make_float4(x[i].x * inv, x[i].y * inv, x[i].z * inv, x[i].w * inv);
+            if (p.blend_from) {
+                const float4 o = load4(p.blend_from + side + 4 * c);
+                v = make_float4((1.f - lambda) * v.x + lambda * o.x, (1.f - lambda) * v.y + lambda * o.y,
+                                (1.f - lambda) * v.z + lambda * o.z, (1.f - lambda) * v.w + lambda * o.w);
+            }
+            if (p.keep_to) store4(p.keep_to + side + 4 * c, v);
+            store4(dst + 4 * c, v);
+        }
+    }
+}
+
 extern "C" int qt_qkv_treat_write(const void* qkv, int in_dtype, int n_splits, long long split_stride, const float* bias,
                                   void* q_out, void* k_cache, void* v_cache, int out_dtype, const int* token_seq,
                                   const int* token_pos, const int* block_table, int max_blocks, int v_norm, float v_eps,
@@ -668,6 +736,17 @@ extern "C" int qt_qkv_treat_write(const void* qkv, int in_dtype, int n_splits, l
     const long long items = (long long)n_tokens * (nq + 2 * nkv);
     const unsigned grid = (unsigned)((items + warps - 1) / warps);
     cudaStream_t s = (cudaStream_t)stream;
+    auto aligned = [](const void* ptr) { return ptr == nullptr || (uintptr_t)ptr % 16 == 0; };
+    const bool vec = d % 4 == 0 && dv % 4 == 0 && d <= 256 && dv <= 256 && split_stride % 4 == 0 && aligned(qkv) && aligned(bias) && aligned(q_out) &&
+                     aligned(k_cache) && aligned(v_cache) && aligned(blend_from) && aligned(keep_to);
+    if (vec) {
+        if (in_dtype == QT_F32 && out_dtype == QT_F32) launch_kernel(qkv_treat_write_vec_kernel<float, float>, dim3(grid), dim3(warps * 32), 0, s, p);
+        else if (in_dtype == QT_F32 && out_dtype == QT_BF16) launch_kernel(qkv_treat_write_vec_kernel<float, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, s, p);
+        else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) launch_kernel(qkv_treat_write_vec_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, s, p);
+        else QT_FAIL(QT_ERR_ARG, "qkv_treat_write: unsupported element types %d -> %d", in_dtype, out_dtype);
+        QT_CHECK_LAUNCH("qkv_treat_write");
+        return QT_OK;
+    }
     if (in_dtype == QT_F32 && out_dtype == QT_F32) launch_kernel(qkv_treat_write_kernel<float, float>, dim3(grid), dim3(warps * 32), 0, s, p);
     else if (in_dtype == QT_F32 && out_dtype == QT_BF16) launch_kernel(qkv_treat_write_kernel<float, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, s, p);
     else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) launch_kernel(qkv_treat_write_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, s, p);

@@ -194,12 +194,13 @@ def test_attention_with_distance_penalty_and_window_edges(dtype, heads, kv_heads
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_values_are_normed_blended_and_cached(dtype):
+@pytest.mark.parametrize("d, dv", [(12, 20), (10, 6), (128, 256), (260, 8)])
+def test_values_are_normed_blended_and_cached(dtype, d, dv):
     """The kernel behind the projection: bias on split sums, q out, k and v into a ring of pages; values divided by
     their root mean square, kept by a source layer and blended by a later one."""
     torch.manual_seed(3)
     store = STORE[dtype]
-    tokens, nq, nkv, d, dv, page, ring = 37, 4, 2, 12, 20, 64, 128
+    tokens, nq, nkv, page, ring = 37, 4, 2, 64, 128
     width = (nq + nkv) * d + nkv * dv
     sums = torch.randn(2, tokens, width, device=DEV)
     bias = torch.randn(width, device=DEV)
