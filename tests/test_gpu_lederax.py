@@ -446,3 +446,24 @@ def test_trace_replay_of_a_folder(tmp_path, dtype, name):
         for row, (key, _) in enumerate(wanted):
             at = lengths[key] - 1 + step["step"]
             close(got[row:row + 1], oracle(model_name, name, False, tuple(requests[key]))[at:at + 1], name, f"step {step['step']} request {key}")
+
+
+def test_trace_replay_of_many_short_requests_at_once(tmp_path):
+    """Forty requests of one to five tokens live together: 120 tokens in all, which --max-tokens states exactly, though
+    every request holds a page of its own."""
+    import json
+    import subprocess
+    import sys
+    import numpy as np
+    model_name = "lederax-tiny-b"
+    folder = model(model_name, "fp32")[0]
+    requests = {f"q{i}": tokens_of(model_name, 1 + i % 5, 300 + i) for i in range(40)}
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": r, "want": [len(r) - 1]} for k, r in requests.items()], "end": list(requests)}]
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(tmp_path),
+                           "--max-tokens", str(sum(len(r) for r in requests.values()))], input=json.dumps(steps[0]) + "\n",
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    got = torch.from_numpy(np.fromfile(tmp_path / "0.f32", dtype="<f4").reshape(40, config_of(model_name).vocab_size).copy())
+    for row, r in enumerate(requests.values()):
+        close(got[row:row + 1], oracle(model_name, "fp32", False, tuple(r))[-1:], "fp32", f"request {row}")
