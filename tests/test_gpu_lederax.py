@@ -467,3 +467,24 @@ def test_trace_replay_of_many_short_requests_at_once(tmp_path):
     got = torch.from_numpy(np.fromfile(tmp_path / "0.f32", dtype="<f4").reshape(40, config_of(model_name).vocab_size).copy())
     for row, r in enumerate(requests.values()):
         close(got[row:row + 1], oracle(model_name, "fp32", False, tuple(r))[-1:], "fp32", f"request {row}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompt_in_passes_and_decoding_across_position_1024(dtype):
+    """A prompt of 1,300 tokens run in passes of 512 tokens (and chunks of 256 for the windowed groups), then a second
+    sequence decoded from 1,000 to 1,060 tokens: the one-token step's page-table width and context bucket change at
+    1,024, and the full-attention layer's keys are cut into more ranges."""
+    name = "lederax-tiny-b"
+    engine = engine_of(name, dtype, peaky=True, max_step_tokens=512)
+    tokens = tokens_of(name, 1300, 21)
+    want = oracle(name, dtype, True, tuple(tokens))
+    picked = [0, 255, 256, 511, 512, 1023, 1024, 1299]
+    slot = engine.new_sequence()
+    close(engine.step([StepEntry(slot, tokens, picked)]), want[picked], dtype, "a prompt in passes")
+    engine.release(slot)
+    slot = engine.new_sequence()
+    rows = [engine.step([StepEntry(slot, tokens[:1000], [999])])]
+    rows += [engine.step([StepEntry(slot, [t], [0])]) for t in tokens[1000:1060]]
+    engine.release(slot)
+    close(torch.cat(rows), want[999:1060], dtype, "decoding across 1,024")
+    engine.check_kernels()
