@@ -2,7 +2,7 @@
 
 Layers whose mixers ask for the same thing (kv heads, head size, all keys or a window of them)
 form a *group* with storage of its own: one key and one value pool
-``[entries, pages, kv_heads, page_tokens, head_dim]`` (values with their own head size where a mixer says so)
+``[entries, pages, kv_heads, page_tokens, head_dim]`` (values with their own head size and head count where a mixer says so)
 shared by the group's entries, one page list
 per sequence for the whole group.  Beside the pools each mixer that asks for it has a fixed-size
 state block per slot, ``[num_slots + 1, *shape]`` (the last row is a spare for padded rows), zeroed when a slot is handed out; the architecture
@@ -101,9 +101,11 @@ class SequenceCache:
         self.dummy_slot = self.num_slots
         if allocate:
             for group in self.groups:
-                shape = (len(group.owners), total_pages + 1, group.request.kv_heads, page_tokens)
-                group.k = torch.zeros((*shape, group.request.head_dim), dtype=dtype, device=device)
-                group.v = torch.zeros((*shape, group.request.v_head_dim or group.request.head_dim), dtype=dtype, device=device)
+                request = group.request
+                shape = (len(group.owners), total_pages + 1, request.kv_heads, page_tokens)
+                group.k = torch.zeros((*shape, request.head_dim), dtype=dtype, device=device)
+                group.v = torch.zeros((shape[0], shape[1], request.v_heads or request.kv_heads, page_tokens,
+                                       request.v_head_dim or request.head_dim), dtype=dtype, device=device)
             for key, request in self._state_requests.items():
                 self._state_of[key] = torch.zeros((self.num_slots + 1, *request.shape), dtype=request.dtype, device=device)
 
@@ -154,5 +156,5 @@ class SequenceCache:
     def token_bytes(self) -> int:
         """Bytes of keys and values one cached token occupies over all full-attention entries."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.owners) * g.request.kv_heads * (g.request.head_dim + (g.request.v_head_dim or g.request.head_dim)) * size
-                   for g in self.groups)
+        return sum(len(g.owners) * (g.request.kv_heads * g.request.head_dim + (g.request.v_heads or g.request.kv_heads) *
+                                    (g.request.v_head_dim or g.request.head_dim)) * size for g in self.groups)

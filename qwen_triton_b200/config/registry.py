@@ -65,7 +65,16 @@ def config_from_dict(raw: Mapping[str, Any]):
 
 
 def load_config(model_path: str | Path):
-    return config_from_dict(load_config_dict(model_path))
+    """The typed configuration of a model folder (or of a config.json).  A design some of whose sizes are no key of
+    the file but the shapes of stored tensors (its class has ``with_tensor_shapes``) is completed from the headers of
+    the folder's safetensors files, where there are any."""
+    config = config_from_dict(load_config_dict(model_path))
+    folder = Path(model_path)
+    folder = folder if folder.is_dir() else folder.parent
+    if hasattr(config, "with_tensor_shapes") and any(folder.glob("*.safetensors")):
+        from ..weights.safetensors_io import Checkpoint      # headers only; nothing is read until a tensor is asked for
+        config = config.with_tensor_shapes({name: tuple(stored.shape) for name, stored in Checkpoint(folder).tensors.items()})
+    return config
 
 
 def preset_names() -> list[str]:

@@ -5,7 +5,10 @@
 // h / (nq / nkv).  Key j is visible to the query at absolute position p iff j <= p and, for a
 // windowed group, j > p - window.  Values may have a head size `dv` of their own.  With `r1`/`r2`
 // (one float per query head each) a score loses r1_h * ln(1 + r2_h * (p - j)): a penalty that grows
-// with the logarithm of the distance, computed in float like the score itself.
+// with the logarithm of the distance, computed in float like the score itself.  With `chunk` > 0 key j is visible
+// only if j / chunk == p / chunk as well (positions counted from the start of the sequence).  The value cache may
+// have fewer heads than the key cache: `nv` value heads, key head g reading value head g % nv (several score maps
+// over one set of values).
 //
 // Counterparts in luozoupi/Qwen-Triton: kernels/flash_attention.py:54-152 (one kernel for both
 // cases, no split, no window) and the masked SDPA branch of modules/attention.py:110-123 with
@@ -29,6 +32,8 @@ struct AttnParams {
     int dv;               // head size of the values
     const float* r1;      // [nq] distance penalty r1 * ln(1 + r2 * distance), or null for none
     const float* r2;
+    int chunk;            // > 0: a query sees only the keys of its own chunk of this many positions, counted from position 0
+    int nv;               // value heads: the values of key head g are those of value head g % nv (nv = nkv: its own)
 };
 
 __device__ __forceinline__ float distance_penalty(float r1, float r2, int distance) { return r1 * logf(1.f + r2 * (float)distance); }
@@ -79,14 +84,16 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
     }
 
     const int p_first = past + q0, p_last = past + q0 + rows - 1;
-    const int key_lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    int key_lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    if (p.chunk > 0) key_lo = max(key_lo, p_first / p.chunk * p.chunk);
+    const int vh = kvh % p.nv;
     for (int k0 = key_lo; k0 <= p_last; k0 += PF_BK) {
         __syncthreads();
         for (int r = warp; r < PF_BK; r += PF_WARPS) {
             const int key = k0 + r;
             if (key <= p_last) {
                 const size_t off = cache_offset(table, key, p.ring_tokens, p.page_tokens, p.nkv, kvh, d);
-                const size_t voff = cache_offset(table, key, p.ring_tokens, p.page_tokens, p.nkv, kvh, dv);
+                const size_t voff = cache_offset(table, key, p.ring_tokens, p.page_tokens, p.nv, vh, dv);
                 for (int c = lane; c < d; c += 32) ks[r * kstride + c] = to_float(kc[off + c]);
                 for (int c = lane; c < dv; c += 32) vs[r * dv + c] = to_float(vc[voff + c]);
             } else {
@@ -102,7 +109,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const 
             const int pos = past + q0 + r;
             float s = 0.f;
             for (int c = 0; c < d; ++c) s += qs[r * d + c] * ks[lane * kstride + c];
-            const bool visible = r < rows && key <= pos && (p.window <= 0 || key > pos - p.window);
+            const bool visible = r < rows && key <= pos && (p.window <= 0 || key > pos - p.window) &&
+                                 (p.chunk <= 0 || key >= pos / p.chunk * p.chunk);
             if (penalised && visible) s -= distance_penalty(r1, r2, pos - key);
             s = visible ? s : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(s));
@@ -159,7 +167,8 @@ static int launch_prefill(const AttnParams& p, int max_q_len, cudaStream_t strea
 }
 
 static int check_common(const char* name, int n_seqs, int nq, int nkv, int d, int dv, const float* r1, const float* r2, int page_tokens,
-                        int ring_tokens, int window) {
+                        int ring_tokens, int window, int chunk, int nv) {
+    QT_REQUIRE(chunk >= 0 && nv > 0 && nkv % nv == 0, "%s: chunk=%d, %d value heads for %d key heads", name, chunk, nv, nkv);
     QT_REQUIRE(n_seqs > 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "%s: bad head counts nq=%d nkv=%d (B=%d)", name, nq, nkv, n_seqs);
     QT_REQUIRE(d > 0 && d <= 256, "%s: head_dim=%d is outside 1..256", name, d);
     QT_REQUIRE(dv > 0 && dv <= 256, "%s: value head_dim=%d is outside 1..256", name, dv);
@@ -172,13 +181,14 @@ static int check_common(const char* name, int n_seqs, int nq, int nkv, int d, in
 extern "C" int qt_attention_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
                                     const int* block_table, int max_blocks, const int* seq_start, const int* seq_past,
                                     int n_seqs, int max_q_len, int nq, int nkv, int d, int page_tokens, int ring_tokens,
-                                    int window, float scale, int dv, const float* r1, const float* r2, void* stream) {
+                                    int window, float scale, int dv, const float* r1, const float* r2, int chunk, int nv, void* stream) {
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
-    int rc = check_common("attention_prefill", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window);
+    if (nv <= 0) nv = nkv;
+    int rc = check_common("attention_prefill", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window, chunk, nv);
     if (rc) return rc;
     QT_REQUIRE(nq <= 65535 && n_seqs <= 65535, "attention_prefill: too many heads or sequences for one launch");
     AttnParams p{q, k_cache, v_cache, out, block_table, max_blocks, seq_start, seq_past, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale,
-                 dv, r1, r2};
+                 dv, r1, r2, chunk, nv};
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "attention_prefill", {
         if (dv <= 64) return launch_prefill<T, 64>(p, max_q_len, s);
@@ -222,7 +232,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     float* red_ml = red_acc + DEC_WARPS * DEC_HEADS * dv; // [DEC_WARPS][DEC_HEADS][2]
 
     const int len = dp.seq_len[seq];
-    const int lo = p.window > 0 ? max(0, len - p.window) : 0;
+    int lo = p.window > 0 ? max(0, len - p.window) : 0;
+    if (p.chunk > 0) lo = max(lo, (len - 1) / p.chunk * p.chunk);
+    const int vh = kvh % p.nv;
     const int span = len - lo;
     const int chunk = (span + dp.n_splits - 1) / dp.n_splits;
     const int k_begin = lo + split * chunk;
@@ -286,7 +298,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
         }
         const int n_keys = min(32, k_end - k0);
         for (int kk = 0; kk < n_keys; ++kk) {
-            const T* vrow = vc + cache_offset(table, k0 + kk, p.ring_tokens, p.page_tokens, p.nkv, kvh, dv);
+            const T* vrow = vc + cache_offset(table, k0 + kk, p.ring_tokens, p.page_tokens, p.nv, vh, dv);
             float v[DMAX / 32];
 #pragma unroll
             for (int j = 0; j < DMAX / 32; ++j) {
@@ -395,15 +407,16 @@ extern "C" int qt_attention_decode(const void* q, const void* k_cache, const voi
                                    const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
                                    int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
                                    int n_splits, float* part_acc, float* part_ml, int dv, const float* r1, const float* r2,
-                                   void* stream) {
+                                   int chunk, int nv, void* stream) {
     if (n_seqs == 0) return QT_OK;
-    int rc = check_common("attention_decode", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window);
+    if (nv <= 0) nv = nkv;
+    int rc = check_common("attention_decode", n_seqs, nq, nkv, d, dv, r1, r2, page_tokens, ring_tokens, window, chunk, nv);
     if (rc) return rc;
     QT_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: n_splits=%d", n_splits);
     QT_REQUIRE(n_splits == 1 || (part_acc && part_ml), "attention_decode: split results need scratch memory");
     QT_REQUIRE(n_seqs <= 65535, "attention_decode: too many sequences for one launch");
     DecodeParams dp{{q, k_cache, v_cache, out, block_table, max_blocks, nullptr, nullptr, n_seqs, nq, nkv, d, page_tokens, ring_tokens, window, scale,
-                     dv, r1, r2},
+                     dv, r1, r2, chunk, nv},
                     seq_len, n_splits, part_acc, part_ml};
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "attention_decode", {

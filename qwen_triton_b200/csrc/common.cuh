@@ -160,6 +160,22 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
     }
 }
 
+// A gate that also treats the up value, with a parameter: g' = min(g, limit), u' = clamp(u, -limit, limit),
+// y = g' sigmoid(1.702 g') (u' + 1).  Its code follows the activations above; the kernels that take `limit` accept it.
+#define QT_ACT_CAPPED 4
+
+// act(g) * u, or the capped gate.
+template <bool FAST>
+__device__ __forceinline__ float gated_value(float g, float u, int act, float limit) {
+    if (act == QT_ACT_CAPPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        const float e = FAST ? __expf(-1.702f * g) : expf(-1.702f * g);
+        return (FAST ? __fdividef(g, 1.f + e) : g / (1.f + e)) * (u + 1.f);
+    }
+    return gate_activation<FAST>(g, act) * u;
+}
+
 // Sum of `n_splits` partial results stored `split_stride` elements apart (split-K GEMM output).
 template <typename T>
 __device__ __forceinline__ float load_sum(const T* base, size_t index, int n_splits, size_t split_stride) {

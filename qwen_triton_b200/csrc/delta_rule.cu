@@ -1,0 +1,363 @@
+// A recurrent mixer: the gated delta rule with one decay per head and key channel, and what surrounds it.
+//
+// Per head, with a state S [dim, vdim] of float that is carried from token to token of a sequence:
+//     S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
+// (the read-out sees the token's own write).  q and k come from kv heads (head h reads kv head h / (heads / kv_heads)),
+// are unit vectors per head (q also times dim^-1/2), and q, k, v have passed a short causal convolution per channel and
+// SiLU.  Everything here is float whatever the model's element type: the projections before it hand over float sums.
+//
+// Kernels, in the order of a step:
+//   delta_prepare_kernel   convolution (its first taps - 1 inputs from the sequence's kept inputs or from zeros), SiLU, unit
+//                          norms, beta = sigmoid(.)
+//   conv_keep_kernel       the last taps - 1 raw inputs of every sequence, kept for its next step
+//   lowrank_kernel         y = f(W2 (x) + bias) for a projection through a few columns (x is a slice of the first
+//                          projection's output): f = exp(-exp(rate_h) softplus(.)) for the decays, sigmoid for a gate
+//   delta_scan_kernel      the recurrence over the tokens of each sequence of the step (any count, one included)
+//   gated_head_norm_kernel o / rms(o) * w * gate per head, into the element type of the output projection's input
+#include "common.cuh"
+
+#include <math.h>
+
+using namespace qt;
+
+constexpr int MAX_TAPS = 16;
+
+struct PrepareParams {
+    const float* proj; int n_splits; size_t split_stride; int proj_cols;    // [splits, T, proj_cols]; columns: q | k | v | beta | ...
+    const float* taps;                // [channels, n_taps], the last column is the current token's
+    const float* kept;                // [slots + 1, n_taps - 1, channels]: raw inputs of the positions just before the step
+    const int* token_seq; const int* token_pos; const int* seq_start; const int* seq_past; const int* slots;
+    float* q; float* k; float* v; float* beta;      // [T, kv_heads, dim] x 2, [T, heads, vdim], [T, heads]
+    int n_tokens, heads, kv_heads, dim, vdim, n_taps;
+    float unit_eps;
+};
+
+__device__ __forceinline__ float sigmoidf(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplusf(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// One warp per (token, item): items 0 .. kv_heads - 1 are the q heads, the next kv_heads the k heads, the next `heads`
+// the v heads, the last one all betas of the token.
+__global__ void __launch_bounds__(128) delta_prepare_kernel(const PrepareParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int items = 2 * p.kv_heads + p.heads + 1;
+    const long long index = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (index >= (long long)p.n_tokens * items) return;
+    const int t = (int)(index / items), item = (int)(index % items);
+    const size_t row = (size_t)t * p.proj_cols;
+    const int channels = 2 * p.kv_heads * p.dim + p.heads * p.vdim;
+    if (item == items - 1) {
+        for (int h = lane; h < p.heads; h += 32)
+            p.beta[(size_t)t * p.heads + h] = sigmoidf(load_sum(p.proj, row + channels + h, p.n_splits, p.split_stride));
+        return;
+    }
+    const int seq = p.token_seq[t];
+    const int local = p.token_pos[t] - p.seq_past[seq];          // tokens of this sequence that the step has run before this one
+    const float* kept = p.kept + (size_t)p.slots[seq] * (p.n_taps - 1) * channels;
+    const bool is_q = item < p.kv_heads, is_k = !is_q && item < 2 * p.kv_heads;
+    const int width = (is_q || is_k) ? p.dim : p.vdim;
+    const int c0 = is_q ? item * p.dim : is_k ? p.kv_heads * p.dim + (item - p.kv_heads) * p.dim
+                                              : 2 * p.kv_heads * p.dim + (item - 2 * p.kv_heads) * p.vdim;
+    float* out = is_q ? p.q + ((size_t)t * p.kv_heads + item) * p.dim
+               : is_k ? p.k + ((size_t)t * p.kv_heads + item - p.kv_heads) * p.dim
+                      : p.v + ((size_t)t * p.heads + item - 2 * p.kv_heads) * p.vdim;
+    float sq = 0.f;
+    for (int i = lane; i < width; i += 32) {
+        const int c = c0 + i;
+        float acc = 0.f;
+        for (int back = 0; back < p.n_taps; ++back) {
+            float x;
+            if (back <= local) x = load_sum(p.proj, row - (size_t)back * p.proj_cols + c, p.n_splits, p.split_stride);
+            else x = kept[(size_t)(p.n_taps - 1 - (back - local)) * channels + c];
+            acc += p.taps[(size_t)c * p.n_taps + p.n_taps - 1 - back] * x;
+        }
+        const float y = acc / (1.f + expf(-acc));
+        out[i] = y;
+        sq += y * y;
+    }
+    if (is_q || is_k) {
+        const float inv = rsqrtf(warp_sum(sq) + p.unit_eps) * (is_q ? rsqrtf((float)p.dim) : 1.f);
+        __syncwarp();
+        for (int i = lane; i < width; i += 32) out[i] *= inv;
+    }
+}
+
+// kept[slot] <- the raw inputs of the sequence's last n_taps - 1 positions after this step.  One thread per
+// (sequence, channel): it reads what it needs of the old rows before it writes.
+__global__ void conv_keep_kernel(const float* __restrict__ proj, int n_splits, size_t split_stride, int proj_cols,
+                                 float* __restrict__ kept, const int* __restrict__ seq_start, const int* __restrict__ slots,
+                                 int n_seqs, int channels, int n_taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int row0 = seq_start[seq], count = seq_start[seq + 1] - row0;
+    float* mine = kept + (size_t)slots[seq] * (n_taps - 1) * channels + c;
+    float value[MAX_TAPS];
+    const int rows = n_taps - 1;
+    for (int j = 0; j < rows; ++j) {
+        const int from = count - rows + j;                       // index among the step's tokens; negative: an older position
+        value[j] = from >= 0 ? load_sum(proj, (size_t)(row0 + from) * proj_cols + c, n_splits, split_stride)
+                             : mine[(size_t)(rows + from) * channels];
+    }
+    for (int j = 0; j < rows; ++j) mine[(size_t)j * channels] = value[j];
+}
+
+// out[t, n] = f(sum_r w[r, n] x[t, r] + bias[n]) for a tile of LR_TOKENS tokens and 256 outputs per block.
+constexpr int LR_TOKENS = 16;
+constexpr int LR_DECAY = 0, LR_SIGMOID = 1;
+
+template <int MODE>
+__global__ void __launch_bounds__(256) lowrank_kernel(const float* __restrict__ proj, int n_splits, size_t split_stride, int proj_cols,
+                                                      int x_offset, int rank, const float* __restrict__ w, const float* __restrict__ bias,
+                                                      const float* __restrict__ rate_log, int per_rate, float* __restrict__ out,
+                                                      int n_tokens, int n_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float xs[];                                 // [LR_TOKENS][rank]
+    const int t0 = blockIdx.y * LR_TOKENS;
+    const int count = min(LR_TOKENS, n_tokens - t0);
+    for (int i = threadIdx.x; i < LR_TOKENS * rank; i += blockDim.x) {
+        const int tt = i / rank, r = i % rank;
+        xs[i] = tt < count ? load_sum(proj, (size_t)(t0 + tt) * proj_cols + x_offset + r, n_splits, split_stride) : 0.f;
+    }
+    __syncthreads();
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= n_out) return;
+    float acc[LR_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < LR_TOKENS; ++tt) acc[tt] = 0.f;
+    for (int r = 0; r < rank; ++r) {
+        const float wv = w[(size_t)r * n_out + n];
+#pragma unroll
+        for (int tt = 0; tt < LR_TOKENS; ++tt) acc[tt] += wv * xs[tt * rank + r];
+    }
+    const float b = bias ? bias[n] : 0.f;
+    const float rate = MODE == LR_DECAY ? expf(rate_log[n / per_rate]) : 0.f;
+#pragma unroll
+    for (int tt = 0; tt < LR_TOKENS; ++tt) {
+        if (tt >= count) break;
+        const float z = acc[tt] + b;
+        out[(size_t)(t0 + tt) * n_out + n] = MODE == LR_DECAY ? expf(-rate * softplusf(z)) : sigmoidf(z);
+    }
+}
+
+// ----------------------------------------------------------------------------- the recurrence
+// grid (column blocks, heads, sequences).  A block of 256 threads owns SCAN_COLS = 32 columns of one head's state; a
+// column belongs to 8 neighbouring lanes, lane s of them holding rows s, s + 8, ... (R of them) in registers.  The
+// tokens' q, k and decays (shared by the block), and the block's v columns and beta, pass through shared memory in chunks
+// of SCAN_CHUNK tokens, the next chunk fetched (cp.async) while this one is worked on.
+constexpr int SCAN_COLS = 32;
+constexpr int SCAN_LANES = 8;
+constexpr int SCAN_CHUNK = 16;
+
+struct ScanParams {
+    const float* q; const float* k; const float* v; const float* beta; const float* decay;
+    float* state;                 // [slots + 1, heads, dim, vdim]
+    float* out;                   // [T, heads, vdim]
+    const int* seq_start; const int* slots;
+    int heads, kv_heads, dim, vdim;
+};
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int R>
+__global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) delta_scan_kernel(const ScanParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int dim = p.dim, vdim = p.vdim;
+    const int per_token = 3 * dim + SCAN_COLS + 1;                 // q, k, decay, the block's v columns, beta
+    float* buffers[2] = {sm, sm + SCAN_CHUNK * per_token};
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int kvh = head / (p.heads / p.kv_heads);
+    const int col = threadIdx.x / SCAN_LANES, sub = threadIdx.x % SCAN_LANES;
+    const int j = blockIdx.x * SCAN_COLS + col;
+    const bool live = j < vdim;
+    const int row0 = p.seq_start[seq], count = p.seq_start[seq + 1] - row0;
+    float* state = p.state + ((size_t)p.slots[seq] * p.heads + head) * dim * vdim;
+
+    float s[R];
+#pragma unroll
+    for (int m = 0; m < R; ++m) {
+        const int i = sub + SCAN_LANES * m;
+        s[m] = (live && i < dim) ? state[(size_t)i * vdim + j] : 0.f;
+    }
+    auto fetch = [&](int chunk, float* buf) {
+        const int first = chunk * SCAN_CHUNK, n = min(SCAN_CHUNK, count - first);
+        for (int e = threadIdx.x; e < n * per_token; e += blockDim.x) {
+            const int tt = e / per_token, c = e % per_token;
+            const size_t t = (size_t)(row0 + first + tt);
+            const float* src;
+            if (c < dim) src = p.q + (t * p.kv_heads + kvh) * dim + c;
+            else if (c < 2 * dim) src = p.k + (t * p.kv_heads + kvh) * dim + (c - dim);
+            else if (c < 3 * dim) src = p.decay + (t * p.heads + head) * dim + (c - 2 * dim);
+            else if (c < 3 * dim + SCAN_COLS) {
+                const int jj = blockIdx.x * SCAN_COLS + (c - 3 * dim);
+                src = p.v + (t * p.heads + head) * vdim + (jj < vdim ? jj : vdim - 1);
+            } else src = p.beta + t * p.heads + head;
+            cp_async4(buf + e, src);
+        }
+        cp_async_commit();
+    };
+    const int chunks = (count + SCAN_CHUNK - 1) / SCAN_CHUNK;
+    if (chunks > 0) fetch(0, buffers[0]);
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+        cp_async_wait_all();
+        __syncthreads();                                           // this chunk has landed; everyone is done with the other buffer
+        if (chunk + 1 < chunks) fetch(chunk + 1, buffers[(chunk + 1) & 1]);
+        const float* buf = buffers[chunk & 1];
+        const int n = min(SCAN_CHUNK, count - chunk * SCAN_CHUNK);
+        for (int tt = 0; tt < n; ++tt) {
+            const float* q = buf + tt * per_token;
+            const float* k = q + dim;
+            const float* g = k + dim;
+            const float vj = q[3 * dim + col], beta = q[3 * dim + SCAN_COLS];
+            float kk[R];
+            float pred = 0.f;
+#pragma unroll
+            for (int m = 0; m < R; ++m) {
+                const int i = sub + SCAN_LANES * m;
+                const bool in = i < dim;
+                kk[m] = in ? k[i] : 0.f;
+                s[m] *= in ? g[i] : 1.f;
+                pred += s[m] * kk[m];
+            }
+            pred += __shfl_xor_sync(0xffffffffu, pred, 1);
+            pred += __shfl_xor_sync(0xffffffffu, pred, 2);
+            pred += __shfl_xor_sync(0xffffffffu, pred, 4);
+            const float u = beta * (vj - pred);
+            float o = 0.f;
+#pragma unroll
+            for (int m = 0; m < R; ++m) {
+                const int i = sub + SCAN_LANES * m;
+                s[m] += kk[m] * u;
+                o += s[m] * (i < dim ? q[i] : 0.f);
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (sub == 0 && live) p.out[((size_t)(row0 + chunk * SCAN_CHUNK + tt) * p.heads + head) * vdim + j] = o;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < R; ++m) {
+        const int i = sub + SCAN_LANES * m;
+        if (live && i < dim) state[(size_t)i * vdim + j] = s[m];
+    }
+}
+
+// out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * gate[t, h, :].  One warp per (token, head).
+template <typename TO>
+__global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __restrict__ o, const float* __restrict__ gate,
+                                                              const float* __restrict__ w, float eps, TO* __restrict__ out,
+                                                              long long items, int vdim) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= items) return;
+    const float* src = o + item * vdim;
+    float sq = 0.f;
+    for (int i = lane; i < vdim; i += 32) { const float x = src[i]; sq += x * x; }
+    const float inv = rsqrtf(warp_sum(sq) / (float)vdim + eps);
+    for (int i = lane; i < vdim; i += 32)
+        out[item * vdim + i] = from_float<TO>(src[i] * inv * w[i] * (gate ? gate[item * vdim + i] : 1.f));
+}
+
+// ----------------------------------------------------------------------------- entry points
+extern "C" int qt_delta_prepare(const float* proj, int n_splits, long long split_stride, int proj_cols, const float* taps,
+                                float* kept, const int* token_seq, const int* token_pos, const int* seq_start,
+                                const int* seq_past, const int* slots, float* q, float* k, float* v, float* beta, int n_tokens,
+                                int n_seqs, int heads, int kv_heads, int dim, int vdim, int n_taps, float unit_eps, void* stream) {
+    QT_REQUIRE(n_tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0,
+               "delta_prepare: bad sizes T=%d heads=%d kv_heads=%d dim=%d vdim=%d", n_tokens, heads, kv_heads, dim, vdim);
+    QT_REQUIRE(n_taps >= 1 && n_taps <= MAX_TAPS, "delta_prepare: a convolution of %d taps (1..%d)", n_taps, MAX_TAPS);
+    const int channels = 2 * kv_heads * dim + heads * vdim;
+    QT_REQUIRE(proj_cols >= channels + heads && n_splits >= 1, "delta_prepare: a projection of %d columns does not hold q, k, v and beta", proj_cols);
+    if (n_tokens == 0) return QT_OK;
+    PrepareParams p{proj, n_splits, (size_t)split_stride, proj_cols, taps, kept, token_seq, token_pos, seq_start, seq_past, slots,
+                    q, k, v, beta, n_tokens, heads, kv_heads, dim, vdim, n_taps, unit_eps};
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long items = (long long)n_tokens * (2 * kv_heads + heads + 1);
+    launch_kernel(delta_prepare_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, p);
+    QT_CHECK_LAUNCH("delta_prepare");
+    if (n_taps > 1) {
+        launch_kernel(conv_keep_kernel, dim3((channels + 127) / 128, n_seqs), dim3(128), 0, s, proj, n_splits, (size_t)split_stride, proj_cols,
+                      kept, seq_start, slots, n_seqs, channels, n_taps);
+        QT_CHECK_LAUNCH("conv_keep");
+    }
+    return QT_OK;
+}
+
+extern "C" int qt_lowrank(const float* proj, int n_splits, long long split_stride, int proj_cols, int x_offset, int rank,
+                          const float* w, const float* bias, const float* rate_log, int per_rate, float* out, int n_tokens,
+                          int n_out, int mode, void* stream) {
+    QT_REQUIRE(n_tokens >= 0 && n_out > 0 && rank > 0 && x_offset >= 0 && x_offset + rank <= proj_cols && n_splits >= 1,
+               "lowrank: bad sizes T=%d N=%d rank=%d at column %d of %d", n_tokens, n_out, rank, x_offset, proj_cols);
+    QT_REQUIRE(mode == LR_SIGMOID || (mode == LR_DECAY && rate_log && per_rate > 0), "lowrank: mode %d", mode);
+    QT_REQUIRE((size_t)LR_TOKENS * rank * sizeof(float) <= 48 * 1024, "lowrank: %d columns are too many for a tile in shared memory", rank);
+    if (n_tokens == 0) return QT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((n_out + 255) / 256, (n_tokens + LR_TOKENS - 1) / LR_TOKENS);
+    const size_t smem = (size_t)LR_TOKENS * rank * sizeof(float);
+    if (mode == LR_DECAY)
+        launch_kernel(lowrank_kernel<LR_DECAY>, grid, dim3(256), smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset, rank, w, bias,
+                      rate_log, per_rate, out, n_tokens, n_out);
+    else
+        launch_kernel(lowrank_kernel<LR_SIGMOID>, grid, dim3(256), smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset, rank, w, bias,
+                      rate_log, per_rate, out, n_tokens, n_out);
+    QT_CHECK_LAUNCH("lowrank");
+    return QT_OK;
+}
+
+template <int R>
+static int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
+    const size_t smem = 2 * (size_t)SCAN_CHUNK * (3 * p.dim + SCAN_COLS + 1) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(delta_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "delta_scan: cannot raise shared memory: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    launch_kernel(delta_scan_kernel<R>, dim3((p.vdim + SCAN_COLS - 1) / SCAN_COLS, p.heads, n_seqs), dim3(SCAN_COLS * SCAN_LANES), smem, s, p);
+    QT_CHECK_LAUNCH("delta_scan");
+    return QT_OK;
+}
+
+extern "C" int qt_delta_scan(const float* q, const float* k, const float* v, const float* beta, const float* decay, float* state,
+                             float* out, const int* seq_start, const int* slots, int n_seqs, int heads, int kv_heads, int dim,
+                             int vdim, void* stream) {
+    QT_REQUIRE(n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && vdim > 0, "delta_scan: bad sizes");
+    QT_REQUIRE(dim > 0 && dim <= 512, "delta_scan: %d key channels per head (1..512)", dim);
+    QT_REQUIRE(n_seqs <= 65535 && heads <= 65535, "delta_scan: too many sequences or heads for one launch");
+    if (n_seqs == 0) return QT_OK;
+    ScanParams p{q, k, v, beta, decay, state, out, seq_start, slots, heads, kv_heads, dim, vdim};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dim <= 32) return launch_scan<4>(p, n_seqs, s);
+    if (dim <= 64) return launch_scan<8>(p, n_seqs, s);
+    if (dim <= 128) return launch_scan<16>(p, n_seqs, s);
+    if (dim <= 256) return launch_scan<32>(p, n_seqs, s);
+    return launch_scan<64>(p, n_seqs, s);
+}
+
+extern "C" int qt_gated_head_norm(const float* o, const float* gate, const float* w, float eps, void* out, int out_dtype,
+                                  int n_tokens, int heads, int vdim, void* stream) {
+    QT_REQUIRE(n_tokens >= 0 && heads > 0 && vdim > 0, "gated_head_norm: bad sizes");
+    if (n_tokens == 0) return QT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long items = (long long)n_tokens * heads;
+    return QT_DISPATCH_DTYPE(out_dtype, "gated_head_norm", {
+        launch_kernel(gated_head_norm_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, o, gate, w, eps, (T*)out, items, vdim);
+        QT_CHECK_LAUNCH("gated_head_norm");
+        return QT_OK;
+    });
+}
+
+QT_DEFINE_LAST_ERROR(delta_rule)

@@ -283,6 +283,88 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     return QT_OK;
 }
 
+// ----------------------------------------------------------------------------- residual add + Dynamic Tanh
+// A norm without statistics: out = tanh(alpha x) * weight + bias, elementwise, alpha one number.  Like the RMSNorm
+// kernels it first folds what is pending into the float stream, here up to two additions (a block whose mixer and
+// feed-forward read the same normed rows adds both results at once), each possibly split-K partial sums in float:
+//   x = residual[src] + sum_s delta_a[s][src] + sum_s delta_b[s][src];  if (!rows) residual[src] = x.
+struct DytParams {
+    float* residual;
+    const float* delta_a; int splits_a; size_t stride_a;
+    const float* delta_b; int splits_b; size_t stride_b;
+    const float* weight; const float* bias; float alpha;
+    void* out; const int* rows; int n_rows, hidden;
+};
+
+template <typename TO>
+__global__ void add_dyt_kernel(const DytParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long total = (long long)p.n_rows * p.hidden;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(idx / p.hidden), i = (int)(idx % p.hidden);
+        const size_t at = (size_t)(p.rows ? p.rows[r] : r) * p.hidden + i;
+        float x = p.residual[at];
+        if (p.delta_a) x += load_sum(p.delta_a, at, p.splits_a, p.stride_a);
+        if (p.delta_b) x += load_sum(p.delta_b, at, p.splits_b, p.stride_b);
+        if (!p.rows) p.residual[at] = x;
+        ((TO*)p.out)[idx] = from_float<TO>(tanhf(p.alpha * x) * p.weight[i] + p.bias[i]);
+    }
+}
+
+extern "C" int qt_add_dyt(float* residual, const float* delta_a, int splits_a, long long stride_a, const float* delta_b, int splits_b,
+                          long long stride_b, const float* weight, const float* bias, float alpha, void* out, int out_dtype,
+                          const int* rows, int n_rows, int hidden, void* stream) {
+    QT_REQUIRE(n_rows >= 0 && hidden > 0 && splits_a >= 1 && splits_b >= 1, "add_dyt: bad sizes rows=%d H=%d", n_rows, hidden);
+    if (n_rows == 0) return QT_OK;
+    DytParams p{residual, delta_a, splits_a, (size_t)stride_a, delta_b, splits_b, (size_t)stride_b, weight, bias, alpha, out, rows, n_rows, hidden};
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)n_rows * hidden;
+    long long blocks = (total + 255) / 256;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+    return QT_DISPATCH_DTYPE(out_dtype, "add_dyt", {
+        launch_kernel(add_dyt_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, s, p);
+        QT_CHECK_LAUNCH("add_dyt");
+        return QT_OK;
+    });
+}
+
+// ----------------------------------------------------------------------------- two attention maps into one head
+// Differential attention: a head has two softmax maps over the same values; ctx holds their results as heads
+// [map][head] (map-major), and the head's output is o = a1 - lambda * a2, divided by its root mean square over the
+// head's values (no weight), times `post`.  One warp per (token, head), float inside.
+template <typename T>
+__global__ void __launch_bounds__(128) map_difference_kernel(const T* __restrict__ ctx, T* __restrict__ out, long long tokens, int heads,
+                                                             int dv, float lambda, float eps, float post) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= tokens * heads) return;
+    const long long t = item / heads;
+    const int h = (int)(item % heads);
+    const T* a1 = ctx + ((size_t)t * 2 * heads + h) * dv;
+    const T* a2 = a1 + (size_t)heads * dv;
+    float sq = 0.f;
+    for (int i = lane; i < dv; i += 32) { const float o = to_float(a1[i]) - lambda * to_float(a2[i]); sq += o * o; }
+    const float inv = rsqrtf(warp_sum(sq) / (float)dv + eps) * post;
+    for (int i = lane; i < dv; i += 32) out[item * dv + i] = from_float<T>((to_float(a1[i]) - lambda * to_float(a2[i])) * inv);
+}
+
+extern "C" int qt_map_difference(const void* ctx, void* out, int dtype, int n_tokens, int heads, int dv, float lambda, float eps,
+                                 float post, void* stream) {
+    QT_REQUIRE(n_tokens >= 0 && heads > 0 && dv > 0, "map_difference: bad sizes");
+    if (n_tokens == 0) return QT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long items = (long long)n_tokens * heads;
+    return QT_DISPATCH_DTYPE(dtype, "map_difference", {
+        launch_kernel(map_difference_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, (const T*)ctx, (T*)out, (long long)n_tokens,
+                      heads, dv, lambda, eps, post);
+        QT_CHECK_LAUNCH("map_difference");
+        return QT_OK;
+    });
+}
+
 // ----------------------------------------------------------------------------- q/k norm + rotary + cache write
 // Input: the fused projection output qkv[t, (nq + 2 nkv) * d] (possibly split-K partial sums).
 // One warp per (token, head):
@@ -302,6 +384,7 @@ struct QkvParams {
     const float* cos_sin; int rotary_dim; int max_pos;
     int n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj;
     int interleaved;        // rotation pairs are (2i, 2i + 1) instead of (i, i + rd/2)
+    int nv, dv;             // value heads and their size (the keys' unless given)
 };
 
 template <typename TI, typename TO, bool VEC>
@@ -310,15 +393,25 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     pdl_wait();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int heads_total = p.nq + (p.kv_in_proj ? 2 * p.nkv : 0);
+    const int heads_total = p.nq + (p.kv_in_proj ? p.nkv + p.nv : 0);
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (item >= (long long)p.n_tokens * heads_total) return;
     const int t = (int)(item / heads_total);
     const int head = (int)(item % heads_total);
     const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
     if (!is_q && !p.write_kv) return;
+    if (!is_q && !is_k && (p.nv != p.nkv || p.dv != p.d)) {
+        // a value head of its own size: summed, stored
+        const int vh = head - p.nq - p.nkv;
+        const size_t cols = (size_t)(p.nq + p.nkv) * p.d + (size_t)p.nv * p.dv;
+        const size_t from = (size_t)t * cols + (size_t)(p.nq + p.nkv) * p.d + (size_t)vh * p.dv;
+        const int* table = p.block_table + (size_t)p.token_seq[t] * p.max_blocks;
+        TO* dst = (TO*)p.v_cache + cache_offset(table, p.token_pos[t], p.ring_tokens, p.page_tokens, p.nv, vh, p.dv);
+        for (int i = lane; i < p.dv; i += 32) dst[i] = from_float<TO>(load_sum((const TI*)p.qkv, from + i, p.n_splits, p.split_stride));
+        return;
+    }
     float* vec = smem + warp * p.d;
-    const size_t in_base = (size_t)t * heads_total * p.d + (size_t)head * p.d;
+    const size_t in_base = (size_t)t * ((size_t)p.nq * p.d + (p.kv_in_proj ? (size_t)p.nkv * p.d + (size_t)p.nv * p.dv : 0)) + (size_t)head * p.d;
     const TI* in = (const TI*)p.qkv;
     const float* w = is_q ? p.q_weight : (is_k ? p.k_weight : nullptr);
 
@@ -518,7 +611,10 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
                                      const int* token_pos, const int* block_table, int max_blocks,
                                      const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
                                      int rotary_dim, int max_pos, int n_tokens, int nq, int nkv, int d, int page_tokens,
-                                     int ring_tokens, int write_kv, int kv_in_proj, int interleaved, void* stream) {
+                                     int ring_tokens, int write_kv, int kv_in_proj, int interleaved, int nv, int dv, void* stream) {
+    if (nv <= 0) nv = nkv;
+    if (dv <= 0) dv = d;
+    const bool own_values = nv != nkv || dv != d;
     QT_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && d <= 1024, "qk_norm_rope_write: bad sizes T=%d nq=%d nkv=%d d=%d", n_tokens, nq, nkv, d);
     QT_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0, "qk_norm_rope_write: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, d);
     QT_REQUIRE(rotary_dim == 0 || (cos_sin && max_pos > 0), "qk_norm_rope_write: rotation needs a cos/sin table");
@@ -527,14 +623,14 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     QT_REQUIRE(!write_kv || kv_in_proj, "qk_norm_rope_write: nothing to write without k and v in the projection");
     if (n_tokens == 0) return QT_OK;
     QkvParams p{qkv, n_splits, (size_t)split_stride, q_out, k_cache, v_cache, token_seq, token_pos, block_table, max_blocks,
-                q_weight, k_weight, eps, cos_sin, rotary_dim, max_pos, n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj, interleaved};
+                q_weight, k_weight, eps, cos_sin, rotary_dim, max_pos, n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj, interleaved, nv, dv};
     const int warps = 4;
-    const long long items = (long long)n_tokens * (nq + (kv_in_proj ? 2 * nkv : 0));
+    const long long items = (long long)n_tokens * (nq + (kv_in_proj ? nkv + nv : 0));
     const unsigned grid = (unsigned)((items + warps - 1) / warps);
     const size_t smem = (size_t)warps * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     // 16-byte loads and stores need head_dim % 8 == 0 (bfloat16 rows of the cache and of q) and aligned bases
-    const bool vec = d % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+    const bool vec = !own_values && d % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
                      (!write_kv || (((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0)));
     // the register form: all dimensions rotate, half a head is one or two rounds of 32 or 64 elements, enough tokens
     // to fill the machine with a few heads per warp
@@ -546,7 +642,7 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     const bool pair_aligned = split_stride % 2 == 0 && ((uintptr_t)qkv % 8 == 0) && ((uintptr_t)q_out % 8 == 0) && ((uintptr_t)cos_sin % 8 == 0) &&
                               (!q_weight || (uintptr_t)q_weight % 8 == 0) && (!k_weight || (uintptr_t)k_weight % 8 == 0) &&
                               (!write_kv || (((uintptr_t)k_cache % 8 == 0) && ((uintptr_t)v_cache % 8 == 0)));
-    if (pe && pair_aligned && n_tokens >= 256 && nq + 2 * nkv <= 65535 * 16 && (in_dtype == QT_F32 || in_dtype == QT_BF16) && out_dtype == QT_BF16) {
+    if (pe && !own_values && pair_aligned && n_tokens >= 256 && nq + 2 * nkv <= 65535 * 16 && (in_dtype == QT_F32 || in_dtype == QT_BF16) && out_dtype == QT_BF16) {
         const int heads_total = nq + (kv_in_proj ? 2 * nkv : 0);
         const dim3 pgrid((unsigned)n_tokens, (unsigned)((heads_total + warps * HEADS_PER_WARP - 1) / (warps * HEADS_PER_WARP)));
 #define QT_LAUNCH_PAIRS(TI, E, IT) launch_kernel(qk_norm_rope_pairs_kernel<TI, __nv_bfloat16, E, IT>, pgrid, dim3(warps * 32), 0, s, p)
@@ -763,7 +859,7 @@ __device__ __forceinline__ size_t gate_column(int i, int group) { return group ?
 
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
-                              long long total, int inter, int group, int act) {
+                              long long total, int inter, int group, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     const int up_offset = group ? group : inter;
@@ -774,7 +870,7 @@ __global__ void swiglu_kernel(const TI* __restrict__ gate_up, int n_splits, size
         const size_t base = (size_t)t * 2 * inter + gate_column(i, group);
         const float g = load_sum(gate_up, base, n_splits, split_stride);
         const float u = load_sum(gate_up, base + up_offset, n_splits, split_stride);
-        out[idx] = from_float<TO>(gate_activation<false>(g, act) * u);
+        out[idx] = from_float<TO>(gated_value<false>(g, u, act, limit));
     }
 }
 
@@ -798,16 +894,17 @@ __device__ __forceinline__ void add4(float4& x, const float4& y) { x.x += y.x; x
 // silu(g) * u.  For a float result the exponential and the division are the library's; for a bfloat16 result
 // (8 bits of mantissa) the hardware approximations (2 ulp of float) are used: with the exact forms the kernel was
 // bound by instruction issue, not by memory.
-template <typename TO> __device__ __forceinline__ float silu_mul(float g, float u, int act) { return gate_activation<false>(g, act) * u; }
-template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u, int act) { return gate_activation<true>(g, act) * u; }
-template <typename TO> __device__ __forceinline__ float4 silu_mul4(const float4& g, const float4& u, int act) {
-    return make_float4(silu_mul<TO>(g.x, u.x, act), silu_mul<TO>(g.y, u.y, act), silu_mul<TO>(g.z, u.z, act), silu_mul<TO>(g.w, u.w, act));
+template <typename TO> __device__ __forceinline__ float silu_mul(float g, float u, int act, float limit) { return gated_value<false>(g, u, act, limit); }
+template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u, int act, float limit) { return gated_value<true>(g, u, act, limit); }
+template <typename TO> __device__ __forceinline__ float4 silu_mul4(const float4& g, const float4& u, int act, float limit) {
+    return make_float4(silu_mul<TO>(g.x, u.x, act, limit), silu_mul<TO>(g.y, u.y, act, limit), silu_mul<TO>(g.z, u.z, act, limit),
+                       silu_mul<TO>(g.w, u.w, act, limit));
 }
 
 // PT chunks per thread, all loads issued before the first store.
 template <typename TI, typename TO, int PT>
 __global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
-                                  int inter, int group, int act) {
+                                  int inter, int group, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     const int chunks = inter >> 3;
@@ -835,14 +932,14 @@ __global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, 
 #pragma unroll
         for (int i = 0; i < PT; ++i) {
             const int c = c0 + i * blockDim.x;
-            if (c < chunks) store8(orow + 8 * c, Float8{silu_mul4<TO>(g[i].a, u[i].a, act), silu_mul4<TO>(g[i].b, u[i].b, act)});
+            if (c < chunks) store8(orow + 8 * c, Float8{silu_mul4<TO>(g[i].a, u[i].a, act, limit), silu_mul4<TO>(g[i].b, u[i].b, act, limit)});
         }
     }
 }
 
 extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long long split_stride, void* out, int out_dtype,
-                         int n_tokens, int inter, int group, int act, void* stream) {
-    QT_REQUIRE(act >= 0 && act < QT_ACT_COUNT, "swiglu: unknown activation code %d", act);
+                         int n_tokens, int inter, int group, int act, float limit, void* stream) {
+    QT_REQUIRE(act >= 0 && act <= QT_ACT_CAPPED, "swiglu: unknown activation code %d", act);
     QT_REQUIRE(n_tokens >= 0 && inter > 0 && n_splits >= 1, "swiglu: bad sizes T=%d I=%d", n_tokens, inter);
     QT_REQUIRE(group >= 0 && (group == 0 || inter % group == 0), "swiglu: rows interleaved in groups of %d do not divide I=%d", group, inter);
     if (n_tokens == 0) return QT_OK;
@@ -859,11 +956,11 @@ extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long l
 #define QT_LAUNCH_SWIGLU(TI, TO)                                                                                              \
     do {                                                                                                                      \
         if (vec && per_thread == 2) launch_kernel(swiglu_vec_kernel<TI, TO, 2>, dim3((unsigned)n_tokens, per_row), dim3(threads), 0, s, \
-                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group, act);              \
+                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group, act, limit);              \
         else if (vec) launch_kernel(swiglu_vec_kernel<TI, TO, 1>, dim3((unsigned)n_tokens, per_row), dim3(threads), 0, s,     \
-                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group, act);              \
+                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group, act, limit);              \
         else launch_kernel(swiglu_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)gate_up, n_splits,  \
-                           (size_t)split_stride, (TO*)out, total, inter, group, act);                                         \
+                           (size_t)split_stride, (TO*)out, total, inter, group, act, limit);                                         \
     } while (0)
     if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_SWIGLU(float, float);
     else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_SWIGLU(float, __nv_bfloat16);

@@ -7,6 +7,11 @@
 // rows streamed once per pair.  Many tokens: the pairs are ordered by expert on the device (count, offsets, scatter;
 // every expert's run padded to whole tiles of rows), and the two products run tile by tile, a tile's rows all of one
 // expert, so that an expert's weights are read once per tile instead of once per pair.
+//
+// The same kernels serve experts chosen by a learned router: without token ids the "table" is read by token (row t
+// holds the experts that a router kernel chose for token t), every pair has a weight of its own (`pair_weights`),
+// an expert may be gated (its first matrix holds [gate; up] rows, mid = gate(g, u)), and a further term
+// row_scale[t] * base[t] (a shared expert behind a gate of one number per token) may be added to the sum.
 #include "common.cuh"
 
 #include <math.h>
@@ -27,10 +32,14 @@ struct ExpertParams {
     float* out;               // [T, width] float
     int n_tokens, vocab, top, experts, width, ff, act;
     float pair_weight;        // weight of every chosen expert (1 / top for an unweighted mean)
+    const float* pair_weights;  // [T, top] a weight per pair instead, or null
+    int gated; float limit;     // up holds [E, 2 ff, width]: ff gate rows, then ff up rows; mid = gated_value(g, u, act, limit)
+    const float* base; int base_splits; size_t base_stride;   // [splits, T, width] float added to out, times row_scale[t]; or null
+    const float* row_scale;     // [T] or null (1)
 };
 
 __device__ __forceinline__ int expert_of(const ExpertParams& p, int t, int k) {
-    int id = p.token_ids[t];
+    int id = p.token_ids ? p.token_ids[t] : t;            // no ids: the table's row t is token t's
     id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id);
     int e = p.table[(size_t)id * p.top + k];
     return e < 0 ? 0 : (e >= p.experts ? p.experts - 1 : e);          // never read outside the weights
@@ -92,12 +101,20 @@ __global__ void __launch_bounds__(EV_WARPS * 32) expert_up_kernel(const ExpertPa
     for (int i = threadIdx.x; i < p.width; i += blockDim.x) xs[i] = to_float(x[i]);
     __syncthreads();
     const int e = expert_of(p, t, k);
-    const T* w = (const T*)p.up + (size_t)e * p.ff * p.width;
+    const T* w = (const T*)p.up + (size_t)e * (p.gated ? 2 : 1) * p.ff * p.width;
     T* mid = (T*)p.mid + (size_t)pair * p.ff;
     const int f0 = (blockIdx.y * EV_WARPS + warp) * EV_FEATS;
     if (f0 >= p.ff) return;
     float acc[EV_FEATS];
     warp_dots<T, VEC>(w + (size_t)f0 * p.width, (size_t)p.width, p.ff - f0, p.width, xs, lane, acc);
+    if (p.gated) {
+        float up[EV_FEATS];
+        warp_dots<T, VEC>(w + (size_t)(p.ff + f0) * p.width, (size_t)p.width, p.ff - f0, p.width, xs, lane, up);
+#pragma unroll
+        for (int j = 0; j < EV_FEATS; ++j)
+            if (lane == 0 && f0 + j < p.ff) mid[f0 + j] = from_float<T>(gated_value<false>(acc[j], up[j], p.act, p.limit));
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < EV_FEATS; ++j)
         if (lane == 0 && f0 + j < p.ff) mid[f0 + j] = from_float<T>(gate_activation<false>(acc[j], p.act));
@@ -124,29 +141,38 @@ __global__ void __launch_bounds__(EV_WARPS * 32) expert_down_kernel(const Expert
         const T* w = (const T*)p.down + (size_t)e * p.width * p.ff;
         float acc[EV_FEATS];
         warp_dots<T, VEC>(w + (size_t)c0 * p.ff, (size_t)p.ff, p.width - c0, p.ff, ms + k * p.ff, lane, acc);
+        const float weight = p.pair_weights ? p.pair_weights[(size_t)t * p.top + k] : 1.f;
 #pragma unroll
-        for (int j = 0; j < EV_FEATS; ++j) total[j] += acc[j];
+        for (int j = 0; j < EV_FEATS; ++j) total[j] += acc[j] * weight;
     }
 #pragma unroll
     for (int j = 0; j < EV_FEATS; ++j)
-        if (lane == 0 && c0 + j < p.width) p.out[(size_t)t * p.width + c0 + j] = total[j] * p.pair_weight;
+        if (lane == 0 && c0 + j < p.width) {
+            const size_t at = (size_t)t * p.width + c0 + j;
+            float y = p.pair_weights ? total[j] : total[j] * p.pair_weight;
+            if (p.base) y += (p.row_scale ? p.row_scale[t] : 1.f) * load_sum(p.base, at, p.base_splits, p.base_stride);
+            p.out[at] = y;
+        }
 }
 
 static int check_experts(const char* name, int n_tokens, int vocab, int top, int experts, int width, int ff, int act) {
     QT_REQUIRE(n_tokens >= 0 && vocab > 0 && top > 0 && experts > 0 && top <= experts, "%s: bad routing sizes T=%d V=%d top=%d E=%d", name, n_tokens, vocab, top, experts);
     QT_REQUIRE(width > 0 && ff > 0, "%s: bad sizes width=%d ff=%d", name, width, ff);
-    QT_REQUIRE(act >= 0 && act < QT_ACT_COUNT, "%s: unknown activation code %d", name, act);
+    QT_REQUIRE(act >= 0 && act <= QT_ACT_CAPPED, "%s: unknown activation code %d", name, act);
     return QT_OK;
 }
 
 extern "C" int qt_experts_by_pair(const void* x, const int* token_ids, const int* table, const void* up, const void* down, void* mid,
                                   float* out, int dtype, int n_tokens, int vocab, int top, int experts, int width, int ff, int act,
-                                  float pair_weight, void* stream) {
+                                  float pair_weight, const float* pair_weights, int gated, float limit, const float* base,
+                                  int base_splits, long long base_stride, const float* row_scale, void* stream) {
+    QT_REQUIRE(gated || act < QT_ACT_COUNT, "experts_by_pair: activation %d needs gated experts", act);
     int rc = check_experts("experts_by_pair", n_tokens, vocab, top, experts, width, ff, act);
     if (rc) return rc;
     if (n_tokens == 0) return QT_OK;
     QT_REQUIRE((size_t)width * 4 <= 200 * 1024 && (size_t)top * ff * 4 <= 200 * 1024, "experts_by_pair: a row of %d or %d x %d floats does not fit shared memory", width, top, ff);
-    ExpertParams p{x, token_ids, table, up, down, mid, out, n_tokens, vocab, top, experts, width, ff, act, pair_weight};
+    ExpertParams p{x, token_ids, table, up, down, mid, out, n_tokens, vocab, top, experts, width, ff, act, pair_weight,
+                   pair_weights, gated, limit, base, base_splits, (size_t)base_stride, row_scale};
     cudaStream_t s = (cudaStream_t)stream;
     const int per_block = EV_WARPS * EV_FEATS;
     return QT_DISPATCH_DTYPE(dtype, "experts_by_pair", {
@@ -228,15 +254,69 @@ __global__ void expert_gather_kernel(const uint4* __restrict__ x, const int* __r
 // out[t, :] = pair_weight * sum_k y[pair_row[t * top + k], :], in float, in the order of k.
 template <typename T>
 __global__ void expert_combine_kernel(const T* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ out, int top, int width,
-                                      float pair_weight) {
+                                      float pair_weight, const float* __restrict__ pair_weights, const float* __restrict__ base,
+                                      int base_splits, size_t base_stride, const float* __restrict__ row_scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc += to_float(y[(size_t)pair_row[t * top + k] * width + c]);
-        out[(size_t)t * width + c] = acc * pair_weight;
+        for (int k = 0; k < top; ++k)
+            acc += to_float(y[(size_t)pair_row[t * top + k] * width + c]) * (pair_weights ? pair_weights[(size_t)t * top + k] : 1.f);
+        if (!pair_weights) acc *= pair_weight;
+        const size_t at = (size_t)t * width + c;
+        if (base) acc += (row_scale ? row_scale[t] : 1.f) * load_sum(base, at, base_splits, base_stride);
+        out[at] = acc;
     }
+}
+
+// A learned router's choice.  logits [splits, T, cols] float (column e < experts: expert e; column `experts`, if
+// shared_gate, the logit of a shared expert's gate).  Scores are sigmoid(logit); the `top` largest are chosen (of equal
+// scores the lower expert first), their weights are the scores over their sum (+ 1e-20) times `scale`.
+// One warp per token; chosen [T, top], weights [T, top], gate [T] = sigmoid of the extra column.
+__global__ void __launch_bounds__(128) route_top_kernel(const float* __restrict__ logits, int n_splits, size_t split_stride, int cols,
+                                                        int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ gate,
+                                                        int n_tokens, int experts, int top, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float route_scores[];                      // [warps][experts]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    float* score = route_scores + (size_t)warp * experts;
+    for (int e = lane; e < experts; e += 32) score[e] = 1.f / (1.f + expf(-load_sum(logits, (size_t)t * cols + e, n_splits, split_stride)));
+    if (gate && lane == 0) gate[t] = 1.f / (1.f + expf(-load_sum(logits, (size_t)t * cols + experts, n_splits, split_stride)));
+    __syncwarp();
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -1.f;
+        int at = experts;
+        for (int e = lane; e < experts; e += 32)
+            if (score[e] > best) { best = score[e]; at = e; }
+        for (int off = 16; off > 0; off >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, off);
+            const int where = __shfl_xor_sync(0xffffffffu, at, off);
+            if (other > best || (other == best && where < at)) { best = other; at = where; }
+        }
+        sum += best;
+        if (lane == 0) { chosen[(size_t)t * top + k] = at; weights[(size_t)t * top + k] = best; score[at] = -2.f; }
+        __syncwarp();
+    }
+    if (lane < top) {
+        for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] = weights[(size_t)t * top + k] / (sum + 1e-20f) * scale;
+    }
+}
+
+extern "C" int qt_route_top(const float* logits, int n_splits, long long split_stride, int cols, int* chosen, float* weights, float* gate,
+                            int n_tokens, int experts, int top, float scale, void* stream) {
+    QT_REQUIRE(n_tokens >= 0 && experts > 0 && top > 0 && top <= experts && cols >= experts + (gate ? 1 : 0) && n_splits >= 1,
+               "route_top: bad sizes T=%d E=%d top=%d cols=%d", n_tokens, experts, top, cols);
+    QT_REQUIRE((size_t)4 * experts * sizeof(float) <= 48 * 1024, "route_top: %d experts are too many for a warp's scores in shared memory", experts);
+    if (n_tokens == 0) return QT_OK;
+    launch_kernel(route_top_kernel, dim3((n_tokens + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), (cudaStream_t)stream, logits, n_splits,
+                  (size_t)split_stride, cols, chosen, weights, gate, n_tokens, experts, top, scale);
+    QT_CHECK_LAUNCH("route_top");
+    return QT_OK;
 }
 
 extern "C" int qt_experts_route(const void* x, const int* token_ids, const int* table, void* ordered, int* pair_row, int* row_token,
@@ -248,7 +328,8 @@ extern "C" int qt_experts_route(const void* x, const int* token_ids, const int* 
     QT_REQUIRE(width % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)ordered % 16 == 0, "experts_route: rows of 16-byte pieces are needed (width=%d)", width);
     QT_REQUIRE(tile_rows > 0 && (long long)max_tiles * tile_rows >= (long long)n_tokens * top, "experts_route: %d tiles of %d rows do not hold the pairs", max_tiles, tile_rows);
     QT_REQUIRE((3 * (size_t)experts + 1) * sizeof(int) <= 48 * 1024, "experts_route: %d experts are too many for one block's counters", experts);
-    ExpertParams p{x, token_ids, table, nullptr, nullptr, nullptr, nullptr, n_tokens, vocab, top, experts, width, 1, 0, 0.f};
+    ExpertParams p{x, token_ids, table, nullptr, nullptr, nullptr, nullptr, n_tokens, vocab, top, experts, width, 1, 0, 0.f,
+                   nullptr, 0, 0.f, nullptr, 1, 0, nullptr};
     cudaStream_t s = (cudaStream_t)stream;
     launch_kernel(expert_route_kernel, dim3(1), dim3(1024), (3 * (size_t)experts + 1) * sizeof(int), s, p, pair_row, row_token, tile_expert, tile_rows, max_tiles);
     QT_CHECK_LAUNCH("expert_route");
@@ -258,12 +339,14 @@ extern "C" int qt_experts_route(const void* x, const int* token_ids, const int* 
 }
 
 extern "C" int qt_experts_combine(const void* y, int dtype, const int* pair_row, float* out, int n_tokens, int top, int width, float pair_weight,
-                                  void* stream) {
+                                  const float* pair_weights, const float* base, int base_splits, long long base_stride,
+                                  const float* row_scale, void* stream) {
     QT_REQUIRE(n_tokens >= 0 && top > 0 && width > 0, "experts_combine: bad sizes T=%d top=%d width=%d", n_tokens, top, width);
     if (n_tokens == 0) return QT_OK;
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "experts_combine", {
-        launch_kernel(expert_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, s, (const T*)y, pair_row, out, top, width, pair_weight);
+        launch_kernel(expert_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, s, (const T*)y, pair_row, out, top, width, pair_weight, pair_weights, base,
+                      base_splits, (size_t)base_stride, row_scale);
         QT_CHECK_LAUNCH("expert_combine");
         return QT_OK;
     });

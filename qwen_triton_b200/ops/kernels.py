@@ -31,21 +31,32 @@ _SIGNATURES = {
                                _c_int, _c_int, _c_ptr],
         "qt_qk_norm_rope_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                   _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
-        "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+        "qt_add_dyt": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int,
+                       _c_int, _c_ptr],
+        "qt_map_difference": [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_ptr],
+    },
+    "delta_rule": {
+        "qt_delta_prepare": [_c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                             _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+        "qt_lowrank": [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_delta_scan": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_gated_head_norm": [_c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "attention": {
         "qt_attention_prefill": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
-                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_attention_decode": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
-                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr],
+                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
     },
     "experts": {
         "qt_experts_by_pair": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                               _c_int, _c_int, _c_int, _c_float, _c_ptr],
+                               _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int, _c_float, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr],
+        "qt_route_top": [_c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr],
         "qt_experts_route": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                              _c_int, _c_ptr],
-        "qt_experts_combine": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+        "qt_experts_combine": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr],
     },
     "experts_tc": {
         "qt_expert_gemm": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
@@ -289,16 +300,19 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
                        q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
                        cos_sin: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
                        page_tokens: int, ring_tokens: int, write_kv: bool = True, kv_in_proj: bool = True,
-                       interleaved: bool = False) -> None:
+                       interleaved: bool = False, v_heads: int | None = None, v_head_dim: int | None = None) -> None:
     """Per-head q/k RMSNorm, rotation and the cache write, from the fused projection output.
 
     qkv [*, T, (nq + 2 nkv) d]; q_out [T, nq, d]; caches [pages, nkv, page_tokens, d]; cos_sin float [P, rd]
     (cos | sin of the rd/2 pair angles); pairs are (i, i + rd/2), or (2i, 2i + 1) with ``interleaved``.
+    With ``v_heads`` / ``v_head_dim`` the values have a head count and size of their own: qkv is then
+    [*, T, (nq + nkv) d + nv dv] and the value cache [pages, nv, page_tokens, dv].
     """
     tokens = qkv.rows
-    width = (num_heads + (2 * num_kv_heads if kv_in_proj else 0)) * head_dim
+    nv, dv = int(v_heads or num_kv_heads), int(v_head_dim or head_dim)
+    width = num_heads * head_dim + ((num_kv_heads * head_dim + nv * dv) if kv_in_proj else 0)
     if qkv.cols != width:
-        raise KernelError(f"qk_norm_rope_write: projection width {qkv.cols} != (nq + 2 nkv) d = {width}")
+        raise KernelError(f"qk_norm_rope_write: projection width {qkv.cols} != nq d + nkv d + nv dv = {width}")
     _need(q_out, "q_out", shape=(tokens, num_heads, head_dim))
     _need(token_seq, "token_seq", torch.int32, (tokens,))
     _need(token_pos, "token_pos", torch.int32, (tokens,))
@@ -313,23 +327,140 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
     if write_kv:
         _need(block_table, "block_table", torch.int32)
         max_blocks = block_table.shape[1]
-        for name, cache in (("k_cache", k_cache), ("v_cache", v_cache)):
+        for name, cache, heads, size in (("k_cache", k_cache, num_kv_heads, head_dim), ("v_cache", v_cache, nv, dv)):
             _need(cache, name, q_out.dtype)
-            if tuple(cache.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
-                raise KernelError(f"{name}: shape {tuple(cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {head_dim}]")
+            if tuple(cache.shape[1:]) != (heads, page_tokens, size):
+                raise KernelError(f"{name}: shape {tuple(cache.shape)} is not [pages, {heads}, {page_tokens}, {size}]")
     _call("elementwise", "qt_qk_norm_rope_write", _ptr(qkv.tensor), _code(qkv.tensor, "qkv"), qkv.n_splits,
           qkv.split_stride, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _code(q_out, "q_out"), _ptr(token_seq),
           _ptr(token_pos), _ptr(block_table), max_blocks, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin),
           rotary_dim, max_pos, tokens, num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens,
-          1 if write_kv else 0, 1 if kv_in_proj else 0, 1 if interleaved else 0, _stream())
+          1 if write_kv else 0, 1 if kv_in_proj else 0, 1 if interleaved else 0, nv, dv, _stream())
+
+
+def add_dyt(residual: torch.Tensor, deltas, weight: torch.Tensor, bias: torch.Tensor, alpha: float, out: torch.Tensor,
+            rows: torch.Tensor | None = None) -> None:
+    """stream += the deltas (up to two ``GemmOut`` of float sums); out = tanh(alpha * stream) * weight + bias.
+
+    Without ``rows`` every row of ``residual`` [T, H] is updated in place and normed into ``out`` [T, H]; with ``rows``
+    (int32 [K]) only those rows are normed into ``out`` [K, H] and the stream is left as it is."""
+    hidden = residual.shape[1]
+    _need(residual, "residual", torch.float32)
+    _need(weight, "weight", torch.float32, (hidden,))
+    _need(bias, "bias", torch.float32, (hidden,))
+    n_rows = residual.shape[0] if rows is None else rows.shape[0]
+    _need(out, "out", shape=(n_rows, hidden))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    deltas = [d for d in deltas if d is not None]
+    if len(deltas) > 2:
+        raise KernelError(f"add_dyt: {len(deltas)} pending additions (at most two)")
+    args = []
+    for delta in deltas + [None] * (2 - len(deltas)):
+        if delta is None:
+            args += [None, 1, 0]
+            continue
+        if not delta.tensor.is_cuda or delta.tensor.dtype != torch.float32 or (delta.rows, delta.cols) != tuple(residual.shape):
+            raise KernelError(f"add_dyt: a delta of {tuple(delta.tensor.shape)} {delta.tensor.dtype} for a float stream {tuple(residual.shape)}")
+        args += [_ptr(delta.tensor), delta.n_splits, delta.split_stride]
+    _call("elementwise", "qt_add_dyt", _ptr(residual), *args, _ptr(weight), _ptr(bias), float(alpha), _ptr(out), _code(out, "out"),
+          _ptr(rows), n_rows, hidden, _stream())
+
+
+def map_difference(ctx: torch.Tensor, out: torch.Tensor, lam: float, eps: float, post: float) -> None:
+    """Two attention maps into one head: ctx [T, 2 * H, dv] holds the maps' results map-major; out [T, H, dv] =
+    unit_rms(ctx[:, h] - lam * ctx[:, H + h]) * post, the root mean square over dv with ``eps`` inside the root."""
+    tokens, heads, dv = out.shape
+    _need(out, "out")
+    _need(ctx, "ctx", out.dtype, (tokens, 2 * heads, dv))
+    _call("elementwise", "qt_map_difference", _ptr(ctx), _ptr(out), _code(out, "out"), tokens, heads, dv, float(lam), float(eps),
+          float(post), _stream())
+
+
+# ----------------------------------------------------------------------------- the gated delta rule
+def delta_prepare(proj: GemmOut, taps: torch.Tensor, kept: torch.Tensor, ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                  beta: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, unit_eps: float) -> None:
+    """What stands between the first projection of a delta-rule mixer and its recurrence, in float: the short causal
+    convolution per channel over q | k | v (``taps`` [channels, n_taps], last column the current token's; the inputs
+    before a step's first token come from ``kept`` [slots + 1, n_taps - 1, channels], which is then brought up to
+    date), SiLU, q and k to unit length per head (``unit_eps`` inside the root; q also times dim^-1/2), and
+    beta = sigmoid of the ``heads`` columns behind q | k | v.  ``ctx`` is the step (sequence and position of every
+    token, the sequences' first rows, lengths before the step and slots)."""
+    tokens = proj.rows
+    channels = 2 * kv_heads * dim + heads * vdim
+    n_taps = taps.shape[1]
+    _need(proj.tensor, "proj", torch.float32)
+    _need(taps, "taps", torch.float32, (channels, n_taps))
+    _need(kept, "kept", torch.float32)
+    if tuple(kept.shape[1:]) != (n_taps - 1, channels):
+        raise KernelError(f"delta_prepare: kept inputs {tuple(kept.shape)} are not [slots, {n_taps - 1}, {channels}]")
+    _need(q, "q", torch.float32, (tokens, kv_heads, dim))
+    _need(k, "k", torch.float32, (tokens, kv_heads, dim))
+    _need(v, "v", torch.float32, (tokens, heads, vdim))
+    _need(beta, "beta", torch.float32, (tokens, heads))
+    _call("delta_rule", "qt_delta_prepare", _ptr(proj.tensor), proj.n_splits, proj.split_stride, proj.cols, _ptr(taps), _ptr(kept),
+          _ptr(ctx.token_seq), _ptr(ctx.token_pos), _ptr(ctx.seq_start), _ptr(ctx.seq_past), _ptr(ctx.slots), _ptr(q), _ptr(k), _ptr(v),
+          _ptr(beta), tokens, ctx.n_seqs, heads, kv_heads, dim, vdim, n_taps, float(unit_eps), _stream(), launches=2 if n_taps > 1 else 1)
+
+
+def lowrank(proj: GemmOut, offset: int, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
+            rate_log: torch.Tensor | None = None, per_rate: int = 0) -> None:
+    """out [T, N] (float) = f(weight^T x + bias) for x = columns ``offset`` .. ``offset + rank`` of ``proj`` and
+    ``weight`` [rank, N] (float, the second matrix of a projection through a few columns, transposed).  With
+    ``rate_log`` [N / per_rate] f is a decay, exp(-exp(rate_log[n / per_rate]) * softplus(.)); else the sigmoid."""
+    rank, n_out = weight.shape
+    _need(proj.tensor, "proj", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out", torch.float32, (proj.rows, n_out))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (n_out,))
+    if rate_log is not None:
+        _need(rate_log, "rate_log", torch.float32, (n_out // max(per_rate, 1),))
+    _call("delta_rule", "qt_lowrank", _ptr(proj.tensor), proj.n_splits, proj.split_stride, proj.cols, int(offset), rank, _ptr(weight),
+          _ptr(bias), _ptr(rate_log), int(per_rate), _ptr(out), proj.rows, n_out, 0 if rate_log is not None else 1, _stream())
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+               out: torch.Tensor, ctx) -> None:
+    """The gated delta rule over the tokens of every sequence of the step, from and into ``state``
+    [slots + 1, heads, dim, vdim] (float): S <- diag(decay_t) S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T;
+    out_t = S^T q_t.  q, k [T, kv_heads, dim]; v, out [T, heads, vdim]; beta [T, heads]; decay [T, heads, dim]."""
+    tokens, heads, vdim = v.shape
+    kv_heads, dim = q.shape[1], q.shape[2]
+    for name, tensor, shape in (("q", q, (tokens, kv_heads, dim)), ("k", k, (tokens, kv_heads, dim)), ("v", v, (tokens, heads, vdim)),
+                                ("beta", beta, (tokens, heads)), ("decay", decay, (tokens, heads, dim)), ("out", out, (tokens, heads, vdim))):
+        _need(tensor, name, torch.float32, shape)
+    _need(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError(f"delta_scan: state {tuple(state.shape)} is not [slots, {heads}, {dim}, {vdim}]")
+    _call("delta_rule", "qt_delta_scan", _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), _ptr(out), _ptr(ctx.seq_start),
+          _ptr(ctx.slots), ctx.n_seqs, heads, kv_heads, dim, vdim, _stream())
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out [T, heads, vdim] = o / sqrt(mean(o^2) + eps) * weight [vdim] * gate, per head; o and gate float."""
+    tokens, heads, vdim = o.shape
+    _need(o, "o", torch.float32)
+    if gate is not None:
+        _need(gate, "gate", torch.float32, (tokens, heads, vdim))
+    _need(weight, "weight", torch.float32, (vdim,))
+    _need(out, "out", shape=(tokens, heads, vdim))
+    _call("delta_rule", "qt_gated_head_norm", _ptr(o), _ptr(gate), _ptr(weight), float(eps), _ptr(out), _code(out, "out"), tokens, heads,
+          vdim, _stream())
 
 
 SWIGLU_GROUP = 16      # rows of gate and of up that alternate in a weight laid out for the GEMM's gated epilogue
 # gate activations of a gated feed-forward, act(gate) * up: names a configuration may use -> the kernels' codes
 ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu": 2, "relu": 3}
+# a gate that also treats the up value and has a parameter ``limit``: g' = min(g, limit), u' = clamp(u, -limit, limit),
+# y = g' sigmoid(1.702 g') (u' + 1).  Taken by ``swiglu`` and the experts' kernels, not by the products' epilogues.
+CAPPED_GATE = "capped_sigmoid"
+_CAPPED_CODE = 4
 
 
-def activation_code(name: str) -> int:
+def activation_code(name: str, capped_ok: bool = False) -> int:
+    if capped_ok and name == CAPPED_GATE:
+        return _CAPPED_CODE
     try:
         return ACTIVATIONS[name]
     except KeyError:
@@ -347,7 +478,7 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torc
     return torch.stack((gate.view(inter // group, group, hidden), up.view(inter // group, group, hidden)), dim=1).reshape(2 * inter, hidden)
 
 
-def swiglu(gate_up: GemmOut, out: torch.Tensor, group: int = 0, activation: str = "silu") -> None:
+def swiglu(gate_up: GemmOut, out: torch.Tensor, group: int = 0, activation: str = "silu", limit: float = 0.0) -> None:
     """out[t, i] = act(gate[t, i]) * up[t, i] where gate_up[t] holds gate then up (``group`` 0) or alternates
     ``group`` elements of gate and ``group`` of up; ``activation`` is one of ``ACTIVATIONS``."""
     tokens, inter = out.shape
@@ -355,7 +486,8 @@ def swiglu(gate_up: GemmOut, out: torch.Tensor, group: int = 0, activation: str 
     if (gate_up.rows, gate_up.cols) != (tokens, 2 * inter):
         raise KernelError(f"swiglu: input {tuple(gate_up.tensor.shape)} does not match output {tuple(out.shape)}")
     _call("elementwise", "qt_swiglu", _ptr(gate_up.tensor), _code(gate_up.tensor, "gate_up"), gate_up.n_splits,
-          gate_up.split_stride, _ptr(out), _code(out, "out"), tokens, inter, int(group), activation_code(activation), _stream())
+          gate_up.split_stride, _ptr(out), _code(out, "out"), tokens, inter, int(group), activation_code(activation, True), float(limit),
+          _stream())
 
 
 # ----------------------------------------------------------------------------- attention
@@ -368,7 +500,7 @@ def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_t
     _need(out, "out", q.dtype, (tokens, num_heads, v_dim))
     if tuple(k_cache.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
         raise KernelError(f"cache shape {tuple(k_cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {head_dim}]")
-    if tuple(v_cache.shape[:-1]) != tuple(k_cache.shape[:-1]):
+    if (v_cache.shape[0], v_cache.shape[2]) != (k_cache.shape[0], k_cache.shape[2]) or num_kv_heads % v_cache.shape[1]:
         raise KernelError(f"value cache {tuple(v_cache.shape)} does not go with key cache {tuple(k_cache.shape)}")
     _need(block_table, "block_table", torch.int32)
     if penalty is not None:
@@ -380,6 +512,15 @@ def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_t
 def _plain_attention(q: torch.Tensor, v_cache: torch.Tensor, penalty) -> bool:
     """Whether every tensor-core attention kernel may take this call: values as wide as keys, no distance penalty."""
     return penalty is None and v_cache.shape[-1] == q.shape[2]
+
+
+def _generic_only(k_cache: torch.Tensor, v_cache: torch.Tensor, chunk, impl: str | None) -> bool:
+    """A mask in chunks, or fewer value heads than key heads: the generic kernels compute these."""
+    if not chunk and v_cache.shape[1] == k_cache.shape[1]:
+        return False
+    if impl not in (None, "generic"):
+        raise KernelError(f"attention kernel {impl!r} does not take a mask in chunks or value heads shared by several key heads")
+    return True
 
 
 def _penalised_choice(q: torch.Tensor, v_cache: torch.Tensor, page_tokens: int, scale: float, impl: str | None, mma: str) -> str:
@@ -426,13 +567,18 @@ def _pick_attention(q: torch.Tensor, page_tokens: int, impl: str | None, prefill
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                       block_table: torch.Tensor, seq_start: torch.Tensor, seq_past: torch.Tensor, max_q_len: int,
                       num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float,
-                      impl: str | None = None, penalty: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
+                      impl: str | None = None, penalty: tuple[torch.Tensor, torch.Tensor] | None = None,
+                      chunk: int | None = None) -> None:
     """Causal attention of packed sequences over the cache (which already holds this step's keys).
+    ``chunk``: a query at position i sees key j only if i // chunk == j // chunk as well.  A value cache with fewer
+    heads than the key cache serves key head g with value head g % (value heads).
     ``impl`` forces a kernel ("tc": tcgen05, "mma": mma.sync, "generic"); by default the shape decides.
     ``penalty`` = (r1, r2), float [heads] each: the score of key j for the query at position i loses
     r1_h * ln(1 + r2_h * (i - j))."""
     _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
-    if not _plain_attention(q, v_cache, penalty):
+    if _generic_only(k_cache, v_cache, chunk, impl):
+        impl = "generic"
+    elif not _plain_attention(q, v_cache, penalty):
         impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "mma")
     n_seqs = seq_past.shape[0]
     _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
@@ -456,7 +602,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
           num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), v_cache.shape[-1],
-          _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, _stream())
+          _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1], _stream())
 
 
 def _ws_merges_in_cluster(n_splits: int, warps: int, group: int, head_dim: int) -> bool:
@@ -475,7 +621,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      block_table: torch.Tensor, seq_len: torch.Tensor, num_kv_heads: int, page_tokens: int,
                      ring_tokens: int, window: int | None, scale: float, n_splits: int,
                      part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, impl: str | None = None,
-                     warps: int = 1, penalty: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
+                     warps: int = 1, penalty: tuple[torch.Tensor, torch.Tensor] | None = None, chunk: int | None = None) -> None:
     """One query token per sequence; ``seq_len`` counts the keys it sees (its own included).
 
     With ``n_splits`` > 1 the keys of each sequence are cut into that many ranges whose partial
@@ -486,7 +632,9 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     """
     n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
-    if not _plain_attention(q, v_cache, penalty):
+    if _generic_only(k_cache, v_cache, chunk, impl):
+        impl = "generic"
+    elif not _plain_attention(q, v_cache, penalty):
         impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "ws")
     if n_splits > 1:
         _need(part_acc, "part_acc", torch.float32)
@@ -511,28 +659,65 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     else:
         _call("attention", "qt_attention_decode", *common[:4], _code(q, "q"), *common[4:], _ptr(part_acc), _ptr(part_ml),
               v_cache.shape[-1], _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None,
-              _stream(), launches=launches)
+              int(chunk or 0), v_cache.shape[1], _stream(), launches=launches)
 
 
 # ----------------------------------------------------------------------------- experts chosen by a table
-def experts_by_pair(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
-                    mid: torch.Tensor, out: torch.Tensor, activation: str, pair_weight: float) -> None:
+def route_top(logits: GemmOut, chosen: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None, experts: int, scale: float) -> None:
+    """A learned router's choice from float logits [*, T, cols]: scores = sigmoid(logits[:, :experts]); ``chosen``
+    [T, top] (int32) the ``top`` largest, ``weights`` [T, top] their scores over their sum (+ 1e-20) times ``scale``;
+    ``gate`` [T] = sigmoid(logits[:, experts]) where given (a shared expert's gate, one number per token)."""
+    tokens, top = chosen.shape
+    _need(logits.tensor, "logits", torch.float32)
+    _need(chosen, "chosen", torch.int32, (logits.rows, top))
+    _need(weights, "weights", torch.float32, (tokens, top))
+    if gate is not None:
+        _need(gate, "gate", torch.float32, (tokens,))
+    _call("experts", "qt_route_top", _ptr(logits.tensor), logits.n_splits, logits.split_stride, logits.cols, _ptr(chosen), _ptr(weights),
+          _ptr(gate), tokens, int(experts), top, float(scale), _stream())
+
+
+def _expert_extras(tokens: int, top: int, width: int, pair_weights, base: GemmOut | None, row_scale):
+    """Checked optional operands of the expert kernels: per-pair weights, a further term and its per-token factor."""
+    if pair_weights is not None:
+        _need(pair_weights, "pair_weights", torch.float32, (tokens, top))
+    if base is not None:
+        _need(base.tensor, "base", torch.float32)
+        if (base.rows, base.cols) != (tokens, width):
+            raise KernelError(f"experts: a further term of {tuple(base.tensor.shape)} for an output of [{tokens}, {width}]")
+    if row_scale is not None:
+        _need(row_scale, "row_scale", torch.float32, (tokens,))
+    return (_ptr(pair_weights), _ptr(base.tensor) if base is not None else None, base.n_splits if base is not None else 1,
+            base.split_stride if base is not None else 0, _ptr(row_scale))
+
+
+def experts_by_pair(x: torch.Tensor, token_ids: torch.Tensor | None, table: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
+                    mid: torch.Tensor, out: torch.Tensor, activation: str, pair_weight: float = 1.0,
+                    pair_weights: torch.Tensor | None = None, gated: bool = False, limit: float = 0.0,
+                    base: GemmOut | None = None, row_scale: torch.Tensor | None = None) -> None:
     """out [T, width] (float) = pair_weight * sum over the ``top`` experts e that ``table[token_ids[t]]`` names of
     down[e] act(up[e] x[t]): one matrix-vector pass per (token, expert) pair, the form for few tokens.
-    up [E, ff, width], down [E, width, ff], mid [T * top, ff] (scratch for the activations), all of x's element type."""
+    up [E, ff, width], down [E, width, ff], mid [T * top, ff] (scratch for the activations), all of x's element type.
+
+    Without ``token_ids`` row t of ``table`` [T, top] names token t's experts (a router's choice).  ``pair_weights``
+    [T, top] weighs every pair by itself.  ``gated``: up is [E, 2 ff, width], ff gate rows then ff up rows, and
+    mid = act(gate) * up, or the capped gate with ``limit``.  ``base`` (float sums [*, T, width]) times
+    ``row_scale`` [T] is added to the result."""
     tokens, width = x.shape
-    experts, ff = up.shape[0], up.shape[1]
+    experts, ff = up.shape[0], up.shape[1] // (2 if gated else 1)
     top = table.shape[1]
     _need(x, "x")
-    _need(token_ids, "token_ids", torch.int32, (tokens,))
+    if token_ids is not None:
+        _need(token_ids, "token_ids", torch.int32, (tokens,))
     _need(table, "table", torch.int32)
-    _need(up, "up", x.dtype, (experts, ff, width))
+    _need(up, "up", x.dtype, (experts, (2 if gated else 1) * ff, width))
     _need(down, "down", x.dtype, (experts, width, ff))
     _need(mid, "mid", x.dtype, (tokens * top, ff))
     _need(out, "out", torch.float32, (tokens, width))
+    weights_ptr, base_ptr, base_splits, base_stride, scale_ptr = _expert_extras(tokens, top, width, pair_weights, base, row_scale)
     _call("experts", "qt_experts_by_pair", _ptr(x), _ptr(token_ids), _ptr(table), _ptr(up), _ptr(down), _ptr(mid), _ptr(out),
-          _code(x, "x"), tokens, table.shape[0], top, experts, width, ff, activation_code(activation), float(pair_weight),
-          _stream(), launches=2)
+          _code(x, "x"), tokens, table.shape[0], top, experts, width, ff, activation_code(activation, gated), float(pair_weight),
+          weights_ptr, 1 if gated else 0, float(limit), base_ptr, base_splits, base_stride, scale_ptr, _stream(), launches=2)
 
 
 EXPERT_TILE_ROWS = 128      # rows of one tile of the tiled expert products (the MMA's M)
@@ -548,37 +733,49 @@ def experts_tiled_supported(x: torch.Tensor, up: torch.Tensor) -> bool:
     return x.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and up.shape[1] % 8 == 0 and up.shape[2] % 8 == 0
 
 
-def experts_tiled(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
+def experts_tiled(x: torch.Tensor, token_ids: torch.Tensor | None, table: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
                   ordered: torch.Tensor, mid: torch.Tensor, y: torch.Tensor, route: torch.Tensor, out: torch.Tensor,
-                  activation: str, pair_weight: float) -> None:
+                  activation: str, pair_weight: float = 1.0, pair_weights: torch.Tensor | None = None, gated: bool = False,
+                  limit: float = 0.0, wide: torch.Tensor | None = None, base: GemmOut | None = None,
+                  row_scale: torch.Tensor | None = None) -> None:
     """The same result as ``experts_by_pair`` for many tokens: the (token, expert) pairs are ordered by expert on the
     device, each expert's run padded to whole tiles of 128 rows, and both products run tile by tile on the tensor
     cores.  Scratch: ``ordered`` [rows, width], ``mid`` [rows, ff], ``y`` [rows, width] (bfloat16) with
-    rows = expert_tiles(T * top, E) * 128, and ``route`` (int32, T * top + rows + rows / 128 words)."""
+    rows = expert_tiles(T * top, E) * 128, and ``route`` (int32, T * top + rows + rows / 128 words); gated experts
+    also ``wide`` [rows, 2 ff] (their first product, before the gate kernel)."""
     tokens, width = x.shape
-    experts, ff = up.shape[0], up.shape[1]
+    experts, ff = up.shape[0], up.shape[1] // (2 if gated else 1)
     top = table.shape[1]
     tiles = expert_tiles(tokens * top, experts)
     rows = tiles * EXPERT_TILE_ROWS
     _need(x, "x", torch.bfloat16)
-    _need(token_ids, "token_ids", torch.int32, (tokens,))
+    if token_ids is not None:
+        _need(token_ids, "token_ids", torch.int32, (tokens,))
     _need(table, "table", torch.int32)
-    _need(up, "up", torch.bfloat16, (experts, ff, width))
+    _need(up, "up", torch.bfloat16, (experts, (2 if gated else 1) * ff, width))
     _need(down, "down", torch.bfloat16, (experts, width, ff))
     _need(ordered, "ordered", torch.bfloat16, (rows, width))
     _need(mid, "mid", torch.bfloat16, (rows, ff))
     _need(y, "y", torch.bfloat16, (rows, width))
     _need(route, "route", torch.int32, (tokens * top + rows + tiles,))
     _need(out, "out", torch.float32, (tokens, width))
+    weights_ptr, base_ptr, base_splits, base_stride, scale_ptr = _expert_extras(tokens, top, width, pair_weights, base, row_scale)
     pair_row, row_token, tile_expert = route[:tokens * top], route[tokens * top:tokens * top + rows], route[tokens * top + rows:]
     status = _status_word(x.device)
     _call("experts", "qt_experts_route", _ptr(x), _ptr(token_ids), _ptr(table), _ptr(ordered), _ptr(pair_row), _ptr(row_token),
           _ptr(tile_expert), tokens, table.shape[0], top, experts, width, EXPERT_TILE_ROWS, tiles, _stream(), launches=2)
-    _call("experts_tc", "qt_expert_gemm", _ptr(ordered), _ptr(up), _ptr(mid), BF16, _ptr(tile_expert), tiles, experts, ff, width,
-          activation_code(activation), _ptr(status), _stream())
+    if gated:
+        _need(wide, "wide", torch.bfloat16, (rows, 2 * ff))
+        _call("experts_tc", "qt_expert_gemm", _ptr(ordered), _ptr(up), _ptr(wide), BF16, _ptr(tile_expert), tiles, experts, 2 * ff, width,
+              -1, _ptr(status), _stream())
+        swiglu(GemmOut(wide.view(1, rows, 2 * ff)), mid, 0, activation, limit)
+    else:
+        _call("experts_tc", "qt_expert_gemm", _ptr(ordered), _ptr(up), _ptr(mid), BF16, _ptr(tile_expert), tiles, experts, ff, width,
+              activation_code(activation), _ptr(status), _stream())
     _call("experts_tc", "qt_expert_gemm", _ptr(mid), _ptr(down), _ptr(y), BF16, _ptr(tile_expert), tiles, experts, width, ff,
           -1, _ptr(status), _stream())
-    _call("experts", "qt_experts_combine", _ptr(y), BF16, _ptr(pair_row), _ptr(out), tokens, top, width, float(pair_weight), _stream())
+    _call("experts", "qt_experts_combine", _ptr(y), BF16, _ptr(pair_row), _ptr(out), tokens, top, width, float(pair_weight),
+          weights_ptr, base_ptr, base_splits, base_stride, scale_ptr, _stream())
 
 
 # ----------------------------------------------------------------------------- matrix product

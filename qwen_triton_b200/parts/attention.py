@@ -17,7 +17,16 @@ Further parameters, each off unless given, for designs that treat scores or valu
 * ``distance_penalty`` = "log": the score of key j for the query at position i loses r1_h ln(1 + r2_h (i - j)),
   with one r1 and r2 per query head (tensors ``names["r1"]``, ``names["r2"]``);
 * ``weight_suffix`` / ``bias_suffix``: what a projection's tensor names add to the projection's name
-  (default ".weight" / ".bias").
+  (default ".weight" / ".bias"); ``norm_suffix``: the same for the q/k norm weights (default ".weight");
+* ``chunk``: a query at position i sees key j <= i only if i // chunk == j // chunk (positions from the sequence's
+  start).  The cache keeps every key, so that another layer may read them under a mask of its own;
+* ``maps`` = 2 with ``diff``: differential attention.  q and k hold two score maps per head, stored head by head
+  as [map 1, map 2]; each map is a softmax attention of its own over the head's one set of values (size
+  ``v_head_dim``), and the head's output is o = a1 - lambda a2, divided by its root mean square (``head_norm_eps``
+  inside the root, no weight), times (1 - diff), with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff from four
+  vectors of the layer (tensors ``names["lq1"]`` ...).  The projections' rows are reordered map-major when loaded,
+  so that map m of head h is query head m * H + h and reads key head m * G + g; the value cache has G heads;
+* ``float_out``: the output projection hands on float sums (for a float residual addition).
 
 Values that are treated (``v_norm``, ``v_blend``, a head size of their own) go with no rotation and no q/k norm:
 bias, treatment and the cache write are then one kernel behind the projection (``kernels.qkv_treat_write``).
@@ -47,9 +56,18 @@ class Attention:
         self.prefix = prefix
         self.runtime = runtime
         self.hidden = int(params["hidden_size"])
-        self.nq = int(params["num_heads"])
-        self.nkv = int(params["num_kv_heads"])
+        self.maps = int(params.get("maps", 1))
+        if self.maps not in (1, 2):
+            raise ValueError(f"{prefix}: {self.maps} score maps per head (1, or 2 for differential attention)")
+        self.heads_out = int(params["num_heads"])                  # heads as the output projection sees them
+        self.v_heads = int(params["num_kv_heads"])                 # value heads
+        self.nq = self.maps * self.heads_out                       # heads as the attention kernels see them: one per map
+        self.nkv = self.maps * self.v_heads
         self.d = int(params["head_dim"])
+        self.chunk = int(params["chunk"]) if params.get("chunk") else None
+        self.diff = float(params.get("diff", 0.0))
+        self.head_norm_eps = float(params.get("head_norm_eps", 1e-6))
+        self.lam = 0.0
         self.scale = float(params.get("scale", self.d ** -0.5))
         self.window = params.get("window")
         self.own_kv = bool(params.get("own_kv", True))
@@ -76,33 +94,48 @@ class Attention:
         self.q_weight = self.k_weight = None
         # values that are treated before they are cached: bias, treatment and cache write are one kernel of their own
         self.treated = self.v_norm_eps is not None or self.v_blend is not None or self.dv != self.d
+        # values of their own shape that are otherwise untouched go with q/k norm and rotation (one kernel writes all)
+        self.own_values = self.treated and self.v_norm_eps is None and self.v_blend is None and not self.bias
+        if self.maps > 1:
+            self.own_values = True
+        if self.own_values:
+            self.treated = False
         if self.treated and (self.qk_norm or not self.own_kv or position_spec.kind != "none"):
-            raise ValueError(f"{prefix}: treated values (v_norm, v_blend, v_head_dim) go with no rotation, no q/k norm and keys of the layer's own")
+            raise ValueError(f"{prefix}: treated values (v_norm, v_blend) go with no rotation, no q/k norm and keys of the layer's own")
+        if self.maps > 1 and (self.bias or self.window or self.penalised):
+            raise ValueError(f"{prefix}: differential attention goes with no bias, window or distance penalty")
         # the mma.sync attention kernels take values as wide as the keys (and compute the distance penalty, given a
         # positive scale); everything else goes to the generic kernels
-        self.mma_scores = self.dv == self.d and (not self.penalised or self.scale > 0)
-        proj_rows = self.nq * self.d + (self.nkv * (self.d + self.dv) if self.own_kv else 0)
-        if self.treated:
+        self.mma_scores = self.dv == self.d and (not self.penalised or self.scale > 0) and not self.own_values and not self.chunk
+        proj_rows = self.nq * self.d + ((self.nkv * self.d + self.v_heads * self.dv) if self.own_kv else 0)
+        if self.own_values:
+            self.qkv = Linear("attn.qkv.own_values", proj_rows, self.hidden, runtime)
+        elif self.treated:
             self.qkv = Linear("attn.qkv.sums", proj_rows, self.hidden, runtime, float_out=True)      # float sums: the bias is added behind it
         else:
             self.qkv = Linear("attn.qkv" + (".biased" if self.bias else ""), proj_rows, self.hidden, runtime, role="qkv", bias=self.bias)
-        self.o = Linear("attn.o" + (".biased" if self.o_bias else ""), self.hidden, self.nq * self.dv, runtime, role="attn_out", bias=self.o_bias)
+        self.float_out = bool(params.get("float_out", False))
+        self.o = Linear("attn.o" + (".biased" if self.o_bias else "") + (".float" if self.float_out else ""), self.hidden,
+                        self.heads_out * self.dv, runtime, role="" if self.float_out else "attn_out", bias=self.o_bias, float_out=self.float_out)
         ws = runtime.workspace
         ws.declare("attn.q", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
         ws.declare("attn.ctx", runtime.max_step_tokens * self.nq * self.dv, runtime.dtype)
+        if self.maps > 1:
+            ws.declare("attn.heads", runtime.max_step_tokens * self.heads_out * self.dv, runtime.dtype)
         ws.declare("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.dv, torch.float32)
         ws.declare("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2, torch.float32)
         self.side_name = "attn.values." + str(params.get("v_blend_key", "first"))
         if self.v_blend is not None:
             ws.declare(self.side_name, runtime.max_step_tokens * self.nkv * self.dv, torch.float32)
         # few tokens: the projection takes rows whose norm factor is still to be applied (``ScaledRows``)
-        self.takes_scaled_rows = self.qkv.fused_capable
+        self.takes_scaled_rows = self.qkv.fused_capable and not self.own_values
 
     # ------------------------------------------------------------------ weights
     @staticmethod
     def _names(params) -> dict[str, str]:
-        n = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm", "r1", "r2", "v_blend_weight")}
+        n = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm", "r1", "r2", "v_blend_weight", "lq1", "lk1", "lq2", "lk2")}
         n["w"], n["b"] = str(params.get("weight_suffix", ".weight")), str(params.get("bias_suffix", ".bias"))
+        n["nw"] = str(params.get("norm_suffix", ".weight"))
         return n
 
     @staticmethod
@@ -116,13 +149,18 @@ class Attention:
     def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
         hidden, nq, nkv, d = (int(params[k]) for k in ("hidden_size", "num_heads", "num_kv_heads", "head_dim"))
         dv = int(params.get("v_head_dim") or d)
+        maps = int(params.get("maps", 1))
         n = cls._names(params)
         own_kv = bool(params.get("own_kv", True))
-        out = {f"{prefix}.{n['q']}{n['w']}": TensorSpec((nq * d, hidden)),
-               f"{prefix}.{n['o']}{n['w']}": TensorSpec((hidden, nq * dv))}
+        std = float(params.get("init_std", 0.02))
+        out = {f"{prefix}.{n['q']}{n['w']}": TensorSpec((maps * nq * d, hidden), init_std=std),
+               f"{prefix}.{n['o']}{n['w']}": TensorSpec((hidden, nq * dv), init_std=std)}
         if own_kv:
-            out[f"{prefix}.{n['k']}{n['w']}"] = TensorSpec((nkv * d, hidden))
-            out[f"{prefix}.{n['v']}{n['w']}"] = TensorSpec((nkv * dv, hidden))
+            out[f"{prefix}.{n['k']}{n['w']}"] = TensorSpec((maps * nkv * d, hidden), init_std=std)
+            out[f"{prefix}.{n['v']}{n['w']}"] = TensorSpec((nkv * dv, hidden), init_std=std)
+        if maps > 1:
+            for name in ("lq1", "lk1", "lq2", "lk2"):
+                out[f"{prefix}.{n[name]}"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=0.0)
         if params.get("bias", False):
             # the reference starts a bias at zero (models/core.py:269-270); random ones so that a bias that is skipped shows
             for name in (("q",) + (("o",) if params.get("o_bias", True) else ()) + (("k", "v") if own_kv else ())):
@@ -137,16 +175,25 @@ class Attention:
             out[f"{prefix}.{n['v_blend_weight']}"] = TensorSpec((), role="vector", init_std=0.08, init_mean=0.4,
                                                                 optional=params.get("v_blend") != "blend")
         if params.get("qk_norm", False):
-            out[f"{prefix}.{n['q_norm']}.weight"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
+            out[f"{prefix}.{n['q_norm']}{n['nw']}"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
             if own_kv:
-                out[f"{prefix}.{n['k_norm']}.weight"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
+                out[f"{prefix}.{n['k_norm']}{n['nw']}"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
         return out
 
     def load(self, source) -> None:
         n, p = self.names, self.prefix
-        rows = [source(f"{p}.{n['q']}{n['w']}")]
+        def map_major(weight: torch.Tensor, heads: int) -> torch.Tensor:
+            """Rows stored [head][map][d] as [map][head][d]: a map is then a head of its own for the kernels."""
+            if self.maps == 1:
+                return weight
+            return weight.view(heads, self.maps, self.d, weight.shape[1]).transpose(0, 1).reshape(weight.shape)
+
+        rows = [map_major(source(f"{p}.{n['q']}{n['w']}"), self.heads_out)]
         if self.own_kv:
-            rows += [source(f"{p}.{n['k']}{n['w']}"), source(f"{p}.{n['v']}{n['w']}")]
+            rows += [map_major(source(f"{p}.{n['k']}{n['w']}"), self.v_heads), source(f"{p}.{n['v']}{n['w']}")]
+        if self.maps > 1:
+            vec = {name: source(f"{p}.{n[name]}").float() for name in ("lq1", "lk1", "lq2", "lk2")}
+            self.lam = float(torch.exp((vec["lq1"] * vec["lk1"]).sum()) - torch.exp((vec["lq2"] * vec["lk2"]).sum())) + self.diff
         self.qkv.set_weight(torch.cat([r.to(self.runtime.dtype) for r in rows], dim=0))
         self.o.set_weight(source(f"{p}.{n['o']}{n['w']}"))
         if self.bias:
@@ -164,9 +211,9 @@ class Attention:
         if self.v_blend == "blend":
             self.blend_weight = to_device(source(f"{p}.{n['v_blend_weight']}"), torch.float32, self.runtime.device).reshape(1)
         if self.qk_norm:
-            self.q_weight = to_device(source(f"{p}.{n['q_norm']}.weight"), torch.float32, self.runtime.device)
+            self.q_weight = to_device(source(f"{p}.{n['q_norm']}{n['nw']}"), torch.float32, self.runtime.device)
             if self.own_kv:
-                self.k_weight = to_device(source(f"{p}.{n['k_norm']}.weight"), torch.float32, self.runtime.device)
+                self.k_weight = to_device(source(f"{p}.{n['k_norm']}{n['nw']}"), torch.float32, self.runtime.device)
         tables = self.runtime.options.setdefault("position_tables", {})
         key = self.position.key() + (self.runtime.max_positions,)
         if key not in tables:
@@ -175,7 +222,8 @@ class Attention:
 
     # ------------------------------------------------------------------ cache
     def cache_request(self) -> KVRequest | None:
-        return KVRequest(self.nkv, self.d, self.window, self.dv if self.dv != self.d else None)
+        return KVRequest(self.nkv, self.d, self.window, self.dv if self.dv != self.d else None,
+                         self.v_heads if self.v_heads != self.nkv else None)
 
     # ------------------------------------------------------------------ run
     def _splits(self, ctx, cache) -> tuple[int, int]:
@@ -189,6 +237,8 @@ class Attention:
         block: the count whose blocks fill whole waves of three blocks per SM nearly as well as the best one.
         """
         span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
+        if self.chunk:
+            span = min(span, self.chunk)
         group = self.nq // self.nkv
         most = max(1, min(_MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
         if self.mma_scores and self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128 and cache.page_tokens == 64:
@@ -254,7 +304,7 @@ class Attention:
                                     cache.page_tokens, cache.ring_tokens, v_norm_eps=self.v_norm_eps,
                                     blend_from=side if self.v_blend == "blend" else None, blend_weight=self.blend_weight,
                                     keep_to=side if self.v_blend == "source" else None, write_kv=write)
-        elif self.qkv.fusable(tokens) and kernels.fused_qkv_supported(self.d, rotary_dim):
+        elif not self.own_values and self.qkv.fusable(tokens) and kernels.fused_qkv_supported(self.d, rotary_dim):
             # few tokens: per-head norm, rotation and the cache write in the projection's epilogue
             self.qkv.into_qkv(x, q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
                               table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv,
@@ -263,15 +313,22 @@ class Attention:
             kernels.qk_norm_rope_write(
                 self.qkv(x), q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
                 table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv, self.d,
-                cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv, interleaved=self.interleaved)
+                cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv, interleaved=self.interleaved,
+                v_heads=self.v_heads if self.own_values else None, v_head_dim=self.dv if self.own_values else None)
         if ctx.is_decode:
             n_splits, warps = self._splits(ctx, cache)
             kernels.attention_decode(q, cache.k, cache.v, out, table, ctx.seq_len, self.nkv, cache.page_tokens,
                                      cache.ring_tokens, self.window, self.scale, n_splits,
                                      ws.view("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.dv),
-                                     ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2), warps=warps, penalty=penalty)
+                                     ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2), warps=warps, penalty=penalty,
+                                     chunk=self.chunk)
         else:
             kernels.attention_prefill(q, cache.k, cache.v, out, table, ctx.seq_start, ctx.seq_past, ctx.max_q_len,
-                                      self.nkv, cache.page_tokens, cache.ring_tokens, self.window, self.scale, penalty=penalty)
-        out = out.view(tokens, self.nq * self.dv)
+                                      self.nkv, cache.page_tokens, cache.ring_tokens, self.window, self.scale, penalty=penalty,
+                                      chunk=self.chunk)
+        if self.maps > 1:
+            heads = ws.view("attn.heads", tokens, self.heads_out, self.dv)
+            kernels.map_difference(out, heads, self.lam, self.head_norm_eps, 1.0 - self.diff)
+            out = heads
+        out = out.view(tokens, self.heads_out * self.dv)
         return DeferredProduct(self.o, out) if self.o.fusable(tokens) else self.o(out)

@@ -71,12 +71,14 @@ def part_class(family: str, spec: PartSpec) -> type:
 @dataclass(frozen=True)
 class KVRequest:
     """Keys and values per token: all of them (``window`` None) or the last ``window``.  Values have the keys' head
-    size unless ``v_head_dim`` gives their own."""
+    size unless ``v_head_dim`` gives their own, and as many heads as the keys unless ``v_heads`` says otherwise
+    (several key heads, one per score map, over one set of values)."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
+    v_heads: int | None = None
 
 
 @dataclass(frozen=True)
@@ -187,6 +189,7 @@ class ResidualStream:
     def __init__(self, residual: torch.Tensor) -> None:
         self.residual = residual
         self._pending: GemmOut | DeferredProduct | None = None
+        self.more: list[GemmOut] = []      # further additions beside ``pending`` (a block whose parts run side by side)
 
     @property
     def pending(self) -> GemmOut | None:
@@ -202,6 +205,21 @@ class ResidualStream:
         if self._pending is not None:
             raise RuntimeError("the residual stream already has a pending addition; apply a norm first")
         self._pending = delta
+
+    def add_beside(self, delta: GemmOut) -> None:
+        """One more addition beside the pending one, for arrangements whose parts all read the same normed rows.  Only a
+        norm that says ``folds_several`` takes these (``take_all``); the others refuse a stream that holds any."""
+        if self._pending is None:
+            self._pending = delta
+        else:
+            self.more.append(delta)
+
+    def take_all(self) -> list[GemmOut]:
+        """Every pending addition, launched if need be; none is pending afterwards."""
+        first = self.pending
+        out = ([first] if first is not None else []) + self.more
+        self._pending, self.more = None, []
+        return out
 
     def take_deferred(self) -> DeferredProduct | None:
         """The pending addition if it is a product not launched yet (it is then no longer pending), else None."""

@@ -85,3 +85,42 @@ class PreNormBlock:
             return
         x = self._normed(self.feed_forward_norm, stream, self.feed_forward)
         stream.add(self.feed_forward.forward(x, ctx))
+
+
+@register_block("parallel")
+class ParallelBlock(PreNormBlock):
+    """One norm, read by the mixer and by the feed-forward alike: h = norm(x); x += mixer(h) + feed_forward(h).
+
+    Both results are left pending on the stream, side by side; the next norm (one that ``folds_several``) adds them
+    in one pass.  The norm's tensors are named by the block parameter ``mixer_norm``; there is no second norm."""
+
+    def __init__(self, layer: LayerSpec, runtime: Runtime) -> None:
+        names = self._names(layer)
+        norm = self._norm_specs(layer)[0]
+        self.mixer_norm = part_class("norm", norm)(norm.params, names["mixer_norm"], runtime)
+        if not getattr(self.mixer_norm, "folds_several", False) and layer.feed_forward is not None:
+            raise ValueError(f"{layer.prefix}: a parallel block needs a norm that folds several pending additions")
+        self.mixer = part_class("mixer", layer.mixer)(layer.mixer.params, names["mixer"], runtime)
+        self.feed_forward_norm = None
+        self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward = part_class("feed_forward", layer.feed_forward)(layer.feed_forward.params, names["feed_forward"], runtime)
+
+    @classmethod
+    def expected_tensors(cls, layer: LayerSpec) -> dict[str, TensorSpec]:
+        names = cls._names(layer)
+        norm = cls._norm_specs(layer)[0]
+        out: dict[str, TensorSpec] = {}
+        out.update(part_class("norm", norm).expected_tensors(norm.params, names["mixer_norm"]))
+        out.update(part_class("mixer", layer.mixer).expected_tensors(layer.mixer.params, names["mixer"]))
+        if layer.feed_forward is not None:
+            out.update(part_class("feed_forward", layer.feed_forward).expected_tensors(layer.feed_forward.params, names["feed_forward"]))
+        return out
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        x = self.mixer_norm.apply(stream)
+        for part, args in ((self.mixer, (x, ctx, cache)), (self.feed_forward, (x, ctx))):
+            if part is None:
+                continue
+            result = part.forward(*args)
+            stream.add_beside(result.run() if hasattr(result, "run") else result)

@@ -1,5 +1,8 @@
 """Dense gated feed-forward: down(act(gate(x)) * up(x)) (qwen_triton/modules/mlp.py:10-22, where act is SiLU;
-here it is a parameter: any of ``kernels.ACTIVATIONS``).
+here it is a parameter: any of ``kernels.ACTIVATIONS``, or ``kernels.CAPPED_GATE`` with ``limit``:
+g' = min(g, limit), u' = clamp(u, -limit, limit), y = g' sigmoid(1.702 g') (u' + 1), computed by the gate kernel
+behind the plain product).  ``weight_suffix`` is what the tensor names add to the projections' names (default
+".weight"); ``float_out`` makes the down projection hand on float sums.
 
 gate and up run as one product over the fused weight [gate; up].  In bfloat16 its rows alternate 16 of gate and
 16 of up, so that the GEMM for many tokens can apply the SiLU gate in its epilogue (one warp then holds both halves
@@ -27,14 +30,23 @@ class GatedMLP:
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
         self.activation = params.get("activation", "silu")
-        if self.activation not in kernels.ACTIVATIONS:
-            raise ValueError(f"{prefix}: gate activation {self.activation!r} is not one of {sorted(kernels.ACTIVATIONS)}")
-        self.names = {k: params.get(k, f"{k}_proj") for k in ("gate", "up", "down")}
-        fused = runtime.dtype == torch.bfloat16 and self.inter % kernels.SWIGLU_GROUP == 0 and self.hidden % 8 == 0
+        self.capped = self.activation == kernels.CAPPED_GATE
+        self.limit = float(params.get("limit", 0.0))
+        if self.activation not in kernels.ACTIVATIONS and not self.capped:
+            raise ValueError(f"{prefix}: gate activation {self.activation!r} is not one of {sorted(kernels.ACTIVATIONS) + [kernels.CAPPED_GATE]}")
+        if self.capped and self.limit <= 0.0:
+            raise ValueError(f"{prefix}: the capped gate needs a positive limit")
+        self.names = self._names(params)
+        # the gate in a product's epilogue: the activations that are a function of the gate value alone
+        fused = runtime.dtype == torch.bfloat16 and self.inter % kernels.SWIGLU_GROUP == 0 and self.hidden % 8 == 0 and not self.capped
         self.group = kernels.SWIGLU_GROUP if fused else 0
-        self.gate_up = Linear("mlp.gate_up", 2 * self.inter, self.hidden, runtime, role="gate")
-        self.down = Linear("mlp.down", self.hidden, self.inter, runtime, role="mlp_out")
-        runtime.workspace.declare("mlp.act", runtime.max_step_tokens * self.inter, runtime.dtype)
+        float_out = bool(params.get("float_out", False))
+        key = str(params.get("buffers", "mlp"))           # several such parts in one layer keep their buffers apart
+        self.gate_up = Linear(f"{key}.gate_up", 2 * self.inter, self.hidden, runtime, role="gate" if fused else "")
+        self.down = Linear(f"{key}.down" + (".float" if float_out else ""), self.hidden, self.inter, runtime,
+                           role="" if float_out else "mlp_out", float_out=float_out)
+        self.act_buffer = f"{key}.act"
+        runtime.workspace.declare(self.act_buffer, runtime.max_step_tokens * self.inter, runtime.dtype)
         # few tokens: the gate in the epilogue of the gate/up product, which then also applies the factor of the norm
         # in front of it (``ScaledRows``)
         self.takes_scaled_rows = bool(self.group) and self.gate_up.fused_capable
@@ -42,20 +54,26 @@ class GatedMLP:
     @classmethod
     def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
         hidden, inter = int(params["hidden_size"]), int(params["intermediate_size"])
-        n = {k: params.get(k, f"{k}_proj") for k in ("gate", "up", "down")}
-        return {f"{prefix}.{n['gate']}.weight": TensorSpec((inter, hidden)),
-                f"{prefix}.{n['up']}.weight": TensorSpec((inter, hidden)),
-                f"{prefix}.{n['down']}.weight": TensorSpec((hidden, inter))}
+        n = cls._names(params)
+        std = float(params.get("init_std", 0.02))
+        return {f"{prefix}.{n['gate']}": TensorSpec((inter, hidden), init_std=std),
+                f"{prefix}.{n['up']}": TensorSpec((inter, hidden), init_std=std),
+                f"{prefix}.{n['down']}": TensorSpec((hidden, inter), init_std=std)}
+
+    @staticmethod
+    def _names(params) -> dict[str, str]:
+        suffix = str(params.get("weight_suffix", ".weight"))
+        return {k: params.get(k, f"{k}_proj") + suffix for k in ("gate", "up", "down")}
 
     def load(self, source) -> None:
         n, p = self.names, self.prefix
-        gate, up = source(f"{p}.{n['gate']}.weight"), source(f"{p}.{n['up']}.weight")
+        gate, up = source(f"{p}.{n['gate']}"), source(f"{p}.{n['up']}")
         self.gate_up.set_weight(kernels.interleave_gate_up(gate.to(self.runtime.dtype), up.to(self.runtime.dtype), self.group))
-        self.down.set_weight(source(f"{p}.{n['down']}.weight"))
+        self.down.set_weight(source(f"{p}.{n['down']}"))
 
     def forward(self, x, ctx):
         tokens = x.shape[0]
-        act = self.runtime.workspace.view("mlp.act", tokens, self.inter)
+        act = self.runtime.workspace.view(self.act_buffer, tokens, self.inter)
         if self.takes_scaled_rows and self.gate_up.fusable(tokens):
             self.gate_up.into_swiglu(x, act, self.activation)
         elif self.group and kernels.gemm_uses_pairs(x, self.gate_up.weight):
@@ -64,7 +82,7 @@ class GatedMLP:
             # a weight whose tiles fill the machine unsplit: the gate in the plain product's epilogue
             kernels.gemm_tc(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation)
         else:
-            kernels.swiglu(self.gate_up(x), act, self.group, self.activation)
+            kernels.swiglu(self.gate_up(x), act, self.group, self.activation, self.limit)
         # few tokens: the down projection is left to the norm behind it, which launches it with the residual addition
         # (and its own preparation) in the product's epilogue
         return DeferredProduct(self.down, act) if self.down.fusable(tokens) else self.down(act)
@@ -165,4 +183,134 @@ class TableExperts:
         else:
             mid = ws.view("experts.mid", pairs, self.inter)
             kernels.experts_by_pair(x, ctx.token_ids, self.table, self.up, self.down, mid, out, self.activation, self.pair_weight)
+        return GemmOut(out.view(1, tokens, self.hidden))
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts:
+    """Experts chosen by a learned router: logits z = W_router h in float, scores sigmoid(z), the ``top`` largest
+    chosen, their weights the scores over their sum (+ 1e-20) times ``route_scale``; the output is the weighted sum of
+    the chosen experts' outputs.  An expert is gated, down(gate(gate_proj h, up_proj h)), with the activation
+    ``activation`` (``kernels.CAPPED_GATE`` with ``limit``, or one of ``kernels.ACTIVATIONS``) and no biases.  With
+    ``shared`` (a dict: ``intermediate_size``, ``limit``) a further expert of the same form runs for every token and is
+    added, times sigmoid(w_gate . h), one number per token; its gate is one more row of the router's product.
+
+    The routing is computed on the device by a kernel behind the router's product, so a step launches the same
+    kernels whatever the tokens are.  Few (token, expert) pairs run as matrix-vector passes per pair, many are
+    ordered by expert and run in tiles on the tensor cores (``experts.cu``, ``experts_tc.cu``), as for experts chosen
+    by a table.
+
+    Parameters: ``hidden_size``, ``expert_size``, ``experts``, ``top``, ``route_scale``, ``activation``, ``limit``,
+    ``shared``, and the tensor-name pieces ``router``, ``expert`` (a format of the expert's number), ``gate``, ``up``,
+    ``down``, ``shared_name``, ``shared_gate``, ``weight_suffix``.
+    """
+
+    graph_safe = True
+
+    def __init__(self, params, prefix: str, runtime: Runtime) -> None:
+        self.prefix = prefix
+        self.runtime = runtime
+        self.params = dict(params)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["expert_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.route_scale = float(params.get("route_scale", 1.0))
+        self.activation = params.get("activation", "silu")
+        self.limit = float(params.get("limit", 0.0))
+        if self.activation not in kernels.ACTIVATIONS and self.activation != kernels.CAPPED_GATE:
+            raise ValueError(f"{prefix}: gate activation {self.activation!r} is not one of {sorted(kernels.ACTIVATIONS) + [kernels.CAPPED_GATE]}")
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"{prefix}: {self.top} experts per token out of {self.experts}")
+        shared = params.get("shared")
+        self.shared = None
+        if shared is not None:
+            self.shared = GatedMLP({"hidden_size": self.hidden, "intermediate_size": int(shared["intermediate_size"]),
+                                    "activation": self.activation, "limit": float(shared.get("limit", self.limit)),
+                                    "gate": params.get("gate", "gate"), "up": params.get("up", "up"), "down": params.get("down", "down"),
+                                    "weight_suffix": params.get("weight_suffix", ".weight"), "float_out": True, "buffers": "experts.shared",
+                                    "init_std": float(params.get("init_std", 0.02))},
+                                   f"{prefix}.{params.get('shared_name', 'shared')}", runtime)
+        self.router = Linear("experts.router", self.experts + (1 if self.shared else 0), self.hidden, runtime, float_out=True)
+        self.up = self.down = None
+        ws = runtime.workspace
+        tokens = runtime.max_step_tokens
+        ws.declare("experts.out", tokens * self.hidden, torch.float32)
+        ws.declare("experts.chosen", tokens * self.top, torch.int32)
+        ws.declare("experts.weights", tokens * self.top, torch.float32)
+        ws.declare("experts.shared_gate", tokens, torch.float32)
+        self.tiled = runtime.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0
+        pairs = tokens * self.top
+        rows = pairs
+        if self.tiled:
+            tiles = kernels.expert_tiles(pairs, self.experts)
+            rows = tiles * kernels.EXPERT_TILE_ROWS
+            ws.declare("experts.ordered", rows * self.hidden, runtime.dtype)
+            ws.declare("experts.y", rows * self.hidden, runtime.dtype)
+            ws.declare("experts.route", pairs + rows + tiles, torch.int32)
+            ws.declare("experts.wide", rows * 2 * self.inter, runtime.dtype)
+        ws.declare("experts.mid", rows * self.inter, runtime.dtype)
+
+    @staticmethod
+    def _tensor_names(params, prefix: str):
+        suffix = str(params.get("weight_suffix", ".weight"))
+        expert = str(params.get("expert", "experts.{}"))
+        names = [tuple(f"{prefix}.{expert.format(e)}.{params.get(k, k)}{suffix}" for k in ("gate", "up", "down"))
+                 for e in range(int(params["experts"]))]
+        shared_gate = f"{prefix}.{params.get('shared_name', 'shared')}.{params.get('shared_gate', 'gate_weight')}"
+        return f"{prefix}.{params.get('router', 'router')}{suffix}", names, shared_gate
+
+    @classmethod
+    def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
+        hidden, inter, experts = int(params["hidden_size"]), int(params["expert_size"]), int(params["experts"])
+        router, names, shared_gate = cls._tensor_names(params, prefix)
+        std = float(params.get("init_std", 0.02))
+        out = {router: TensorSpec((experts, hidden), init_std=float(params.get("router_init_std", 0.1)))}
+        for gate, up, down in names:
+            out[gate] = TensorSpec((inter, hidden), init_std=std)
+            out[up] = TensorSpec((inter, hidden), init_std=std)
+            out[down] = TensorSpec((hidden, inter), init_std=std)
+        shared = params.get("shared")
+        if shared is not None:
+            sub = {"hidden_size": hidden, "intermediate_size": int(shared["intermediate_size"]), "gate": params.get("gate", "gate"),
+                   "up": params.get("up", "up"), "down": params.get("down", "down"), "weight_suffix": params.get("weight_suffix", ".weight"),
+                   "init_std": std}
+            out.update(GatedMLP.expected_tensors(sub, f"{prefix}.{params.get('shared_name', 'shared')}"))
+            out[shared_gate] = TensorSpec((1, hidden), init_std=float(params.get("router_init_std", 0.1)))
+        return out
+
+    def load(self, source) -> None:
+        router, names, shared_gate = self._tensor_names(self.params, self.prefix)
+        dtype, device = self.runtime.dtype, self.runtime.device
+        self.up = torch.stack([torch.cat((source(gate).to(dtype), source(up).to(dtype)), dim=0).to(device) for gate, up, _ in names]).contiguous()
+        self.down = torch.stack([source(down).to(device=device, dtype=dtype) for _, _, down in names]).contiguous()
+        rows = [source(router).to(dtype)]
+        if self.shared is not None:
+            self.shared.load(source)
+            rows.append(source(shared_gate).to(dtype).reshape(1, self.hidden))
+        self.router.set_weight(torch.cat(rows, dim=0))
+
+    def forward(self, x, ctx) -> GemmOut:
+        tokens = x.shape[0]
+        ws = self.runtime.workspace
+        out = ws.view("experts.out", tokens, self.hidden)
+        chosen = ws.view("experts.chosen", tokens, self.top)
+        weights = ws.view("experts.weights", tokens, self.top)
+        gate = ws.view("experts.shared_gate", tokens) if self.shared is not None else None
+        kernels.route_top(self.router(x), chosen, weights, gate, self.experts, self.route_scale)
+        base = None
+        if self.shared is not None:
+            base = self.shared.forward(x, ctx)
+            base = base.run() if hasattr(base, "run") else base
+        pairs = tokens * self.top
+        if self.tiled and pairs > min(_PAIRS_BY_PAIR, 2 * self.experts):
+            tiles = kernels.expert_tiles(pairs, self.experts)
+            rows = tiles * kernels.EXPERT_TILE_ROWS
+            kernels.experts_tiled(x, None, chosen, self.up, self.down, ws.view("experts.ordered", rows, self.hidden),
+                                  ws.view("experts.mid", rows, self.inter), ws.view("experts.y", rows, self.hidden),
+                                  ws.view("experts.route", pairs + rows + tiles), out, self.activation, pair_weights=weights, gated=True,
+                                  limit=self.limit, wide=ws.view("experts.wide", rows, 2 * self.inter), base=base, row_scale=gate)
+        else:
+            kernels.experts_by_pair(x, None, chosen, self.up, self.down, ws.view("experts.mid", pairs, self.inter), out, self.activation,
+                                    pair_weights=weights, gated=True, limit=self.limit, base=base, row_scale=gate)
         return GemmOut(out.view(1, tokens, self.hidden))

@@ -55,6 +55,8 @@ class RMSNorm:
         epilogue; no norm kernel runs.
         """
         ws = self.runtime.workspace
+        if stream.more:
+            raise RuntimeError(f"{self.name}: this norm folds one pending addition; the stream holds {1 + len(stream.more)}")
         deferred = stream.take_deferred()
         if deferred is not None:
             count = stream.residual.shape[0]
@@ -71,4 +73,58 @@ class RMSNorm:
         kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out, rows, self.groups)
         if rows is None:
             stream.pending = None
+        return out
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh:
+    """A norm that takes no statistics: y = tanh(alpha * x) * w + b with one number ``alpha`` and vectors w, b.
+
+    Parameters: ``size``; the tensor-name pieces ``suffix`` (weight, default ".weight"), ``bias_suffix`` (".bias") and
+    ``alpha_suffix`` (".alpha").  It folds every pending addition of the stream (``folds_several``: a block whose mixer
+    and feed-forward read the same rows leaves two), which must be float sums."""
+
+    graph_safe = True
+    folds_several = True
+    offers_scaled_rows = False
+
+    def __init__(self, params, name: str, runtime: Runtime) -> None:
+        self.size = int(params["size"])
+        self.name = name
+        self.runtime = runtime
+        self.tensors = self._tensor_names(params, name)
+        self.weight = self.bias = None
+        self.alpha = 1.0
+        runtime.workspace.declare("normed", runtime.max_step_tokens * self.size, runtime.dtype)
+
+    @staticmethod
+    def _tensor_names(params, name: str) -> tuple[str, str, str]:
+        return (name + str(params.get("suffix", ".weight")), name + str(params.get("bias_suffix", ".bias")),
+                name + str(params.get("alpha_suffix", ".alpha")))
+
+    @classmethod
+    def expected_tensors(cls, params, name: str) -> dict[str, TensorSpec]:
+        weight, bias, alpha = cls._tensor_names(params, name)
+        size = int(params["size"])
+        return {weight: TensorSpec((size,), role="vector", init_std=0.1, init_mean=1.0),
+                bias: TensorSpec((size,), role="vector", init_std=0.05, init_mean=0.0),
+                alpha: TensorSpec((), role="vector", init_std=0.05, init_mean=0.6)}
+
+    def load(self, source) -> None:
+        weight, bias, alpha = self.tensors
+        self.weight = to_device(source(weight), torch.float32, self.runtime.device)
+        self.bias = to_device(source(bias), torch.float32, self.runtime.device)
+        self.alpha = float(source(alpha).float().reshape(-1)[0])          # read once, when the model is loaded
+
+    def apply(self, stream: ResidualStream, rows: torch.Tensor | None = None, lazy: bool = False):
+        deltas = stream.take_all() if rows is None else ([stream.pending] if stream.pending is not None else []) + stream.more
+        count = stream.residual.shape[0] if rows is None else rows.shape[0]
+        out = self.runtime.workspace.view("normed", count, self.size)
+        while len(deltas) > 2:             # the kernel adds two; a third is folded by a pass of its own
+            kernels.add_dyt(stream.residual, deltas[:2], self.weight, self.bias, self.alpha, self.runtime.workspace.view(
+                "normed", stream.residual.shape[0], self.size))
+            if rows is not None:
+                raise RuntimeError(f"{self.name}: more than two pending additions while only listed rows are wanted")
+            deltas = deltas[2:]
+        kernels.add_dyt(stream.residual, deltas, self.weight, self.bias, self.alpha, out, rows)
         return out
