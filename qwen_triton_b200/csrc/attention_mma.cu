@@ -98,7 +98,8 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
                                       const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
                                       int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
                                       int n_splits, int warps, float* part_acc, float* part_ml, const float* r1, const float* r2,
-                                      void* stream) {
+                                      int chunk, int nv, void* stream) {
+    QT_REQUIRE(chunk >= 0 && nv >= 0 && (nv == 0 || nkv % nv == 0), "attention_decode_ws: chunk=%d, %d value heads for %d key heads", chunk, nv, nkv);
     if (n_seqs == 0) return QT_OK;
     int rc = check("attention_decode_ws", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
     if (rc) return rc;
@@ -118,7 +119,7 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
     QT_REQUIRE(n_splits == 1 || cluster || (part_acc && part_ml), "attention_decode_ws: split results need scratch memory");
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, nullptr, nullptr, seq_len, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                n_splits, part_acc, part_ml, 2, cluster ? 1 : 0, r1, r2};
+                n_splits, part_acc, part_ml, 2, cluster ? 1 : 0, r1, r2, chunk, nv};
     const size_t smem = rings + (cluster ? inboxes : 0);
     dim3 grid(n_splits, nkv * ((group + 15) / 16), n_seqs), block(32 * warps);
     cudaStream_t s = (cudaStream_t)stream;
@@ -150,7 +151,8 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
 extern "C" int qt_attention_prefill_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                         const int* block_table, int max_blocks, const int* seq_start, const int* seq_past,
                                         int n_seqs, int max_q_len, int nq, int nkv, int d, int page_tokens, int ring_tokens,
-                                        int window, float scale, const float* r1, const float* r2, void* stream) {
+                                        int window, float scale, const float* r1, const float* r2, int chunk, int nv, void* stream) {
+    QT_REQUIRE(chunk >= 0 && nv >= 0 && (nv == 0 || nkv % nv == 0), "attention_prefill_mma: chunk=%d, %d value heads for %d key heads", chunk, nv, nkv);
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
     int rc = check("attention_prefill_mma", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
     if (rc) return rc;
@@ -158,7 +160,7 @@ extern "C" int qt_attention_prefill_mma(const void* q, const void* k_cache, cons
     QT_REQUIRE(r1 == nullptr || scale > 0.f, "attention_prefill_mma: with a distance penalty the score scale must be positive");
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, seq_start, seq_past, nullptr, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                1, nullptr, nullptr, 2, 0, r1, r2};
+                1, nullptr, nullptr, 2, 0, r1, r2, chunk, nv};
     const int lds = d + PAD;
     const size_t smem = (size_t)4 * PAGE * lds * 2;
     dim3 grid((max_q_len + PF_BQ - 1) / PF_BQ, nq, n_seqs);

@@ -49,7 +49,13 @@ struct MmaParams {
     // (r1 / (scale * log2 e)) * log2(1 + r2 * distance) before the row maximum, so the scale must be positive.
     const float* r1 = nullptr;
     const float* r2 = nullptr;
+    // A mask in chunks: a query at position i sees key j <= i only if i / chunk == j / chunk (0: no chunks).
+    int chunk = 0;
+    // Value heads: the value cache is [pages, nv, 64, d] and key head g reads value head g % nv (0: nv = nkv).
+    int nv = 0;
 };
+
+__device__ __forceinline__ int chunk_start(int pos, int chunk) { return chunk > 0 ? pos / chunk * chunk : 0; }
 
 __device__ __forceinline__ float penalty_log2(float coefficient, float r2, int distance) {
     return coefficient * __log2f(fmaf(r2, (float)distance, 1.f));
@@ -161,7 +167,8 @@ __global__ void __launch_bounds__(128, 3) attention_decode_mma_kernel(const MmaP
     const uint32_t kv0 = smem_u32(smem_raw) + q_bytes;                               // stages of (K tile, V tile)
 
     const int len = p.seq_len[seq];
-    const int lo = p.window > 0 ? max(0, len - p.window) : 0;
+    const int lo = max(p.window > 0 ? max(0, len - p.window) : 0, chunk_start(len - 1, p.chunk));
+    const int nv = p.nv > 0 ? p.nv : p.nkv, vh = kvh % nv;
     const int first_page = lo / PAGE, last_page = (len - 1) / PAGE;
     const int n_pages = last_page - first_page + 1;
     const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
@@ -177,7 +184,7 @@ __global__ void __launch_bounds__(128, 3) attention_decode_mma_kernel(const MmaP
             const size_t off = ((size_t)page * p.nkv + kvh) * PAGE * d;
             const uint32_t dst = kv0 + (uint32_t)(tile % stages) * 2u * tile_bytes;
             copy.start(dst, p.k_cache + off);
-            copy.start(dst + tile_bytes, p.v_cache + off);
+            copy.start(dst + tile_bytes, p.v_cache + ((size_t)page * nv + vh) * PAGE * d);
         }
         cp_async_commit();
     };
@@ -389,7 +396,8 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
     const uint32_t ring0 = smem_u32(smem_raw) + q_bytes + (uint32_t)warp * 4u * tile_bytes;   // [stage][K tile, V tile]
 
     const int len = p.seq_len[seq];
-    const int lo = p.window > 0 ? max(0, len - p.window) : 0;
+    const int lo = max(p.window > 0 ? max(0, len - p.window) : 0, chunk_start(len - 1, p.chunk));
+    const int nv = p.nv > 0 ? p.nv : p.nkv, vh = kvh % nv;
     const int first_tile = lo / WS_TILE, last_tile = (len - 1) / WS_TILE;
     const int per_stream = (last_tile - first_tile + n_streams) / n_streams;
     const int tile_begin = first_tile + stream * per_stream;
@@ -412,7 +420,7 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
             const size_t off = (((size_t)page * p.nkv + kvh) * PAGE + (t32 & 1) * WS_TILE) * d;
             const uint32_t dst = ring0 + (uint32_t)(tile & 1) * 2u * tile_bytes;
             copy.template start<DMAX, EXACT>(dst, p.k_cache + off);
-            copy.template start<DMAX, EXACT>(dst + tile_bytes, p.v_cache + off);
+            copy.template start<DMAX, EXACT>(dst + tile_bytes, p.v_cache + (((size_t)page * nv + vh) * PAGE + (t32 & 1) * WS_TILE) * d);
         }
         cp_async_commit();
     };
@@ -644,7 +652,8 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw + 2 * tile_bytes);   // [64][lds]
 
     const int p_first = past + q0, p_last = past + q0 + rows - 1;
-    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    const int lo = max(p.window > 0 ? max(0, p_first - p.window + 1) : 0, chunk_start(p_first, p.chunk));
+    const int nv = p.nv > 0 ? p.nv : p.nkv, vh = kvh % nv;
     const int page_begin = lo / PAGE, n_tiles = p_last / PAGE - page_begin + 1;
 
     for (int i = tid; i < PF_BQ * (d >> 3); i += 128) {                              // query tile, rows beyond the sequence zero
@@ -660,7 +669,7 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
             const size_t off = ((size_t)page * p.nkv + kvh) * PAGE * d;
             const uint32_t dst = kv0 + (uint32_t)(tile & 1) * 2u * tile_bytes;
             copy.start(dst, p.k_cache + off);
-            copy.start(dst + tile_bytes, p.v_cache + off);
+            copy.start(dst + tile_bytes, p.v_cache + ((size_t)page * nv + vh) * PAGE * d);
         }
         cp_async_commit();
     };
@@ -679,6 +688,8 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
     // absolute positions of this thread's two query rows; rows beyond the sequence act as its last row
     const int qpos[2] = {min(past + q0 + warp * 16 + g, p_last), min(past + q0 + warp * 16 + g + 8, p_last)};
     const int warp_pos_min = min(past + q0 + warp * 16, p_last), warp_pos_max = min(past + q0 + warp * 16 + 15, p_last);
+    const int qlo[2] = {chunk_start(qpos[0], p.chunk), chunk_start(qpos[1], p.chunk)};         // first key of each row's chunk
+    const int warp_lo_min = chunk_start(warp_pos_min, p.chunk), warp_lo_max = chunk_start(warp_pos_max, p.chunk);
 
     for (int tile = 0; tile < n_tiles; ++tile) {
         issue(tile + 1);
@@ -686,7 +697,7 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
         __syncthreads();
         const uint32_t k_s = kv0 + (uint32_t)(tile & 1) * 2u * tile_bytes, v_s = k_s + tile_bytes;
         const int pos0 = (page_begin + tile) * PAGE;
-        const bool any_visible = pos0 <= warp_pos_max && (p.window <= 0 || pos0 + PAGE - 1 > warp_pos_min - p.window);
+        const bool any_visible = pos0 <= warp_pos_max && (p.window <= 0 || pos0 + PAGE - 1 > warp_pos_min - p.window) && pos0 + PAGE - 1 >= warp_lo_min;
         if (any_visible) {
             float s[8][4];
 #pragma unroll
@@ -710,7 +721,7 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
             // Scores stay unscaled; the scale is folded into the exponent: p = 2^(s * scale2 - m * scale2), one FMA
             // and one ex2 per score.  Most tiles lie wholly below the diagonal (and inside the window) for every row
             // of the warp and need no mask.
-            const bool all_visible = pos0 + PAGE - 1 <= warp_pos_min && (p.window <= 0 || pos0 > warp_pos_max - p.window);
+            const bool all_visible = pos0 + PAGE - 1 <= warp_pos_min && (p.window <= 0 || pos0 > warp_pos_max - p.window) && pos0 >= warp_lo_max;
             if (PEN) {                                               // keys ahead of a row's query are overwritten by the mask below
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt)
@@ -726,7 +737,7 @@ __global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const Mma
                     for (int e = 0; e < 4; ++e) {
                         const int pos = pos0 + nt * 8 + 2 * t + (e & 1);
                         const int qp = qpos[e >> 1];
-                        const bool visible = pos <= qp && (p.window <= 0 || pos > qp - p.window);
+                        const bool visible = pos <= qp && (p.window <= 0 || pos > qp - p.window) && pos >= qlo[e >> 1];
                         if (!visible) s[nt][e] = -INFINITY;
                     }
             }

@@ -57,6 +57,8 @@ struct TcAttnParams {
     const int* block_table; int max_blocks;
     const int* seq_start; const int* seq_past;
     int nq, nkv, ring_tokens, window;
+    int chunk;      // > 0: a query sees only the keys of its own chunk of this many positions, counted from position 0
+    int nv;         // value heads: key head g reads value head g % nv
     float scale;
     int* status;
     const float* r1;               // [nq] factors of the distance penalty (PEN), else null
@@ -170,7 +172,8 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
     const int kvh = head / (p.nq / p.nkv);
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
     const int p_first = past + q0, p_last = past + q0 + rows - 1;
-    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    const int lo = max(p.window > 0 ? max(0, p_first - p.window + 1) : 0, p.chunk > 0 ? p_first / p.chunk * p.chunk : 0);
+    const int vh = kvh % p.nv;
     const int tile_begin = lo / BKEY;
     const int n_tiles = p_last / BKEY - tile_begin + 1;
 
@@ -238,7 +241,7 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
                 if (!mbar_wait(v_empty + 8 * s, phase ^ 1u, status, 1)) break;
                 mbar_expect_tx(v_full + 8 * s, KV_BYTES);
                 for (int pg = 0; pg < PAGES; ++pg) {
-                    const int row0 = (cache_page(table, p.max_blocks, (tile_begin + j) * PAGES + pg, p.ring_tokens) * p.nkv + kvh) * PAGE;
+                    const int row0 = (cache_page(table, p.max_blocks, (tile_begin + j) * PAGES + pg, p.ring_tokens) * p.nv + vh) * PAGE;
                     for (int h = 0; h < HALVES; ++h)
                         tma_load_2d(v_s + s * KV_BYTES + h * KEY_HALF_BYTES + pg * (PAGE * 128), &map_v, v_full + 8 * s, h * 64, row0);
                 }
@@ -293,6 +296,8 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
         const int r = quarter * 32 + lane;                 // this thread's query row = its tensor-memory lane
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int qpos = min(past + q0 + r, p_last);       // rows beyond the sequence act as its last row
+        const int qlo = p.chunk > 0 ? qpos / p.chunk * p.chunk : 0;          // first key of the row's chunk
+        const int last_lo = p.chunk > 0 ? p_last / p.chunk * p.chunk : 0;
         const float scale2 = p.scale * LOG2E;
         const float pen_c = PEN ? -p.r1[head] / scale2 : 0.f, pen_r2 = PEN ? -p.r2[head] : 0.f;     // negated once, for the FMAs
         float m_run = -INFINITY, l_run = 0.f;              // the maximum this row scales by (scaled base-2 domain) and its sum
@@ -319,14 +324,14 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
                         v[q][c] = __float_as_uint(fmaf(pen_c, fast_log2(fmaf(pen_r2, (float)(q * 32 + c), first)), __uint_as_float(v[q][c])));
             }
             // mask only where some row of the block cannot see the whole tile
-            const bool masked = pos0 + BKEY - 1 > p_first || (p.window > 0 && pos0 <= p_last - p.window);
+            const bool masked = pos0 + BKEY - 1 > p_first || (p.window > 0 && pos0 <= p_last - p.window) || pos0 < last_lo;
             if (masked) {
 #pragma unroll
                 for (int q = 0; q < QUARTERS; ++q)
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const int pos = pos0 + q * 32 + c;
-                        if (!(pos <= qpos && (p.window <= 0 || pos > qpos - p.window))) v[q][c] = 0xff800000u;   // -inf
+                        if (!(pos <= qpos && (p.window <= 0 || pos > qpos - p.window) && pos >= qlo)) v[q][c] = 0xff800000u;   // -inf
                     }
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -447,6 +452,7 @@ extern "C" int qt_attention_prefill_tc(const void* q, const void* k_cache, const
                                        int n_pages, const int* block_table, int max_blocks, const int* seq_start,
                                        const int* seq_past, int n_seqs, int max_q_len, int nq, int nkv, int d,
                                        int page_tokens, int ring_tokens, int window, float scale, const float* r1, const float* r2,
+                                       int chunk, int nv,
                                        int* status, void* stream) {
     if (n_seqs == 0 || max_q_len == 0) return QT_OK;
     QT_REQUIRE(n_seqs > 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill_tc: bad head counts nq=%d nkv=%d (B=%d)", nq, nkv, n_seqs);
@@ -465,9 +471,11 @@ extern "C" int qt_attention_prefill_tc(const void* q, const void* k_cache, const
     if (rc) return rc;
     rc = tensor_map(&map_k, k_cache, (uint64_t)n_pages * nkv * PAGE, (uint64_t)d, PAGE);
     if (rc) return rc;
-    rc = tensor_map(&map_v, v_cache, (uint64_t)n_pages * nkv * PAGE, (uint64_t)d, PAGE);
+    if (nv <= 0) nv = nkv;
+    QT_REQUIRE(chunk >= 0 && nkv % nv == 0, "attention_prefill_tc: chunk=%d, %d value heads for %d key heads", chunk, nv, nkv);
+    rc = tensor_map(&map_v, v_cache, (uint64_t)n_pages * nv * PAGE, (uint64_t)d, PAGE);
     if (rc) return rc;
-    TcAttnParams p{(__nv_bfloat16*)out, block_table, max_blocks, seq_start, seq_past, nq, nkv, ring_tokens, window, scale, status, r1, r2};
+    TcAttnParams p{(__nv_bfloat16*)out, block_table, max_blocks, seq_start, seq_past, nq, nkv, ring_tokens, window, chunk, nv, scale, status, r1, r2};
     cudaStream_t s = (cudaStream_t)stream;
     // key tiles of one page, two blocks per SM: measured 12-22 % faster than tiles of two pages with one block per SM
     if (r1) {

@@ -65,13 +65,13 @@ _SIGNATURES = {
         "qt_attention_decode_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
         "qt_attention_decode_ws": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
-                                   _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+                                   _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_attention_prefill_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
-                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr],
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
     },
     "attention_tc": {
         "qt_attention_prefill_tc": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
-                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
     },
     "gemm_simt": {
         "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
@@ -514,13 +514,10 @@ def _plain_attention(q: torch.Tensor, v_cache: torch.Tensor, penalty) -> bool:
     return penalty is None and v_cache.shape[-1] == q.shape[2]
 
 
-def _generic_only(k_cache: torch.Tensor, v_cache: torch.Tensor, chunk, impl: str | None) -> bool:
-    """A mask in chunks, or fewer value heads than key heads: the generic kernels compute these."""
-    if not chunk and v_cache.shape[1] == k_cache.shape[1]:
-        return False
-    if impl not in (None, "generic"):
-        raise KernelError(f"attention kernel {impl!r} does not take a mask in chunks or value heads shared by several key heads")
-    return True
+def _special_mask(k_cache: torch.Tensor, v_cache: torch.Tensor, chunk) -> bool:
+    """A mask in chunks, or fewer value heads than key heads: every kernel computes these but the block-tile decode
+    kernel ("mma" for one-token steps)."""
+    return bool(chunk) or v_cache.shape[1] != k_cache.shape[1]
 
 
 def _penalised_choice(q: torch.Tensor, v_cache: torch.Tensor, page_tokens: int, scale: float, impl: str | None, mma: str) -> str:
@@ -576,9 +573,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     ``penalty`` = (r1, r2), float [heads] each: the score of key j for the query at position i loses
     r1_h * ln(1 + r2_h * (i - j))."""
     _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
-    if _generic_only(k_cache, v_cache, chunk, impl):
-        impl = "generic"
-    elif not _plain_attention(q, v_cache, penalty):
+    if not _plain_attention(q, v_cache, penalty):
         impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "mma")
     n_seqs = seq_past.shape[0]
     _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
@@ -590,14 +585,14 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _call("attention_tc", "qt_attention_prefill_tc", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), q.shape[0],
               k_cache.shape[0], _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs,
               int(max_q_len), num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale),
-              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None,
+              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1],
               _ptr(_status_word(q.device)), _stream())
         return
     if choice == "mma":
         _call("attention_mma", "qt_attention_prefill_mma", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out),
               _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
               num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale),
-              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, _stream())
+              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1], _stream())
         return
     _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
@@ -632,9 +627,9 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     """
     n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens, penalty)
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
-    if _generic_only(k_cache, v_cache, chunk, impl):
-        impl = "generic"
-    elif not _plain_attention(q, v_cache, penalty):
+    if impl == "mma" and _special_mask(k_cache, v_cache, chunk):
+        raise KernelError("the block-tile decode kernel takes no mask in chunks and no value heads shared by several key heads")
+    if not _plain_attention(q, v_cache, penalty):
         impl = _penalised_choice(q, v_cache, page_tokens, scale, impl, "ws")
     if n_splits > 1:
         _need(part_acc, "part_acc", torch.float32)
@@ -653,7 +648,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         launches = 1
     if picked == "ws":
         _call("attention_mma", "qt_attention_decode_ws", *common, int(warps), _ptr(part_acc), _ptr(part_ml),
-              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, _stream(), launches=launches)
+              _ptr(penalty[0]) if penalty else None, _ptr(penalty[1]) if penalty else None, int(chunk or 0), v_cache.shape[1],
+              _stream(), launches=launches)
     elif picked == "mma":
         _call("attention_mma", "qt_attention_decode_mma", *common, _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
     else:

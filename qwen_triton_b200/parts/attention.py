@@ -106,7 +106,7 @@ class Attention:
             raise ValueError(f"{prefix}: differential attention goes with no bias, window or distance penalty")
         # the mma.sync attention kernels take values as wide as the keys (and compute the distance penalty, given a
         # positive scale); everything else goes to the generic kernels
-        self.mma_scores = self.dv == self.d and (not self.penalised or self.scale > 0) and not self.own_values and not self.chunk
+        self.mma_scores = self.dv == self.d and (not self.penalised or self.scale > 0)
         proj_rows = self.nq * self.d + ((self.nkv * self.d + self.v_heads * self.dv) if self.own_kv else 0)
         if self.own_values:
             self.qkv = Linear("attn.qkv.own_values", proj_rows, self.hidden, runtime)
@@ -192,7 +192,8 @@ class Attention:
         if self.own_kv:
             rows += [map_major(source(f"{p}.{n['k']}{n['w']}"), self.v_heads), source(f"{p}.{n['v']}{n['w']}")]
         if self.maps > 1:
-            vec = {name: source(f"{p}.{n[name]}").float() for name in ("lq1", "lk1", "lq2", "lk2")}
+            # one number for the layer, made once on the host (the same bits wherever the tensors were drawn)
+            vec = {name: source(f"{p}.{n[name]}").double().cpu() for name in ("lq1", "lk1", "lq2", "lk2")}
             self.lam = float(torch.exp((vec["lq1"] * vec["lk1"]).sum()) - torch.exp((vec["lq2"] * vec["lk2"]).sum())) + self.diff
         self.qkv.set_weight(torch.cat([r.to(self.runtime.dtype) for r in rows], dim=0))
         self.o.set_weight(source(f"{p}.{n['o']}{n['w']}"))

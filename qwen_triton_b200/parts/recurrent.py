@@ -108,10 +108,9 @@ class GatedDeltaRule:
                n["decay_bias"]: TensorSpec((heads * dim,), role="vector", init_std=0.5, init_mean=-3.0),
                n["decay_rate"]: TensorSpec((heads,), role="vector", init_std=0.3, init_mean=0.0),
                n["norm"]: TensorSpec((vdim,), role="vector", init_std=0.1, init_mean=1.0)}
-        if taps > 1:
-            out[n["q_conv"]] = TensorSpec((kv_heads * dim, taps), role="vector", init_std=0.3, init_mean=0.3)
-            out[n["k_conv"]] = TensorSpec((kv_heads * dim, taps), role="vector", init_std=0.3, init_mean=0.3)
-            out[n["v_conv"]] = TensorSpec((heads * vdim, taps), role="vector", init_std=0.3, init_mean=0.3)
+        # a convolution of one tap is a factor per channel; a model may leave such tensors out (all ones)
+        for key, channels in (("q_conv", kv_heads * dim), ("k_conv", kv_heads * dim), ("v_conv", heads * vdim)):
+            out[n[key]] = TensorSpec((channels, taps), role="vector", init_std=0.3, init_mean=0.3, optional=taps == 1)
         return out
 
     def load(self, source) -> None:
@@ -123,10 +122,11 @@ class GatedDeltaRule:
             rows.append(torch.zeros(self.proj_rows - used, self.hidden, dtype=dtype, device=rows[0].device))
         self.proj.set_weight(torch.cat(rows, dim=0))
         self.o.set_weight(source(n["o"]))
-        if self.taps > 1:
-            conv = torch.cat([source(n[key + "_conv"]).float() for key in ("q", "k", "v")], dim=0)
-        else:
-            conv = torch.ones(self.channels, 1)
+        pieces = []
+        for key, channels in (("q", self.kv_heads * self.dim), ("k", self.kv_heads * self.dim), ("v", self.heads * self.vdim)):
+            stored = source(n[key + "_conv"])
+            pieces.append(stored.float().cpu() if stored is not None else torch.ones(channels, self.taps))
+        conv = torch.cat(pieces, dim=0)
         self.conv = to_device(conv, torch.float32, device)
         # the narrow projections' second matrices: float, transposed to [rank, N] so that neighbouring threads read neighbouring outputs
         self.decay_out = to_device(source(n["decay_out"]).float().t(), torch.float32, device)

@@ -69,7 +69,7 @@ def short_conv(x, taps):
     """Causal convolution per channel: y[t, c] = sum_d taps[c, K - 1 - d] x[t - d, c], zeros before the start."""
     count = taps.shape[1]
     out = torch.zeros_like(x)
-    for d in range(count):
+    for d in range(min(count, x.shape[0])):
         out[d:] += x[:x.shape[0] - d] * taps[:, count - 1 - d]
     return out
 
@@ -85,9 +85,13 @@ def channel_delta(h, tensors, prefix, mixer, eps):
     get = lambda name: tensors[f"{prefix}.{name}"].to(h.dtype)
     tokens = h.shape[0]
     silu = torch.nn.functional.silu
-    q = silu(short_conv(h @ get("q").T, get("q.conv"))).view(tokens, kv_heads, dim)
-    k = silu(short_conv(h @ get("k").T, get("k.conv"))).view(tokens, kv_heads, dim)
-    v = silu(short_conv(h @ get("v").T, get("v.conv"))).view(tokens, heads, vdim)
+    def conv(name, x):                       # a model whose convolutions have one tap may leave the tensors out
+        taps = tensors.get(f"{prefix}.{name}.conv")
+        return short_conv(x, taps.to(h.dtype)) if taps is not None else x
+
+    q = silu(conv("q", h @ get("q").T)).view(tokens, kv_heads, dim)
+    k = silu(conv("k", h @ get("k").T)).view(tokens, kv_heads, dim)
+    v = silu(conv("v", h @ get("v").T)).view(tokens, heads, vdim)
     q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = torch.sigmoid(h @ get("b").T)                                            # [T, heads]

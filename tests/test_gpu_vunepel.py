@@ -1,0 +1,576 @@
+"""The Vunepel design on the GPU against the plain implementation of ``plain_vunepel.py``: each mechanism's kernel alone
+at sizes of its own, then whole models (the two presets and a third made here; they differ in every size, in the order
+of the layers and in which options are absent, equal or 1) whole, token by token, in portions, in unequal batches with
+slots used again, in long decoding across chunk and page edges, and through the generation entry point.  Where random
+weights would hide a fault the inputs are made so that it shows: keys just inside and just outside a chunk that carry
+the softmax, a far key that carries it, page tables in scrambled order with garbage in unused room, a state that must
+survive hundreds of tokens."""
+import functools
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_vunepel as plain
+from qwen_triton_b200 import Engine, QwenB200ForCausalLM, StepEntry, config_from_dict, load_preset, write_random_model
+from qwen_triton_b200.ops import kernels
+from qwen_triton_b200.ops.kernels import GemmOut
+from qwen_triton_b200.weights import Checkpoint, write_safetensors
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ROOT = Path(__file__).resolve().parent.parent
+DTYPES = ("fp32", "bf16")
+STORE = {"fp32": torch.float32, "bf16": torch.bfloat16}
+TOL = {"fp32": dict(atol=2e-4, rtol=2e-4), "bf16": dict(atol=5e-2, rtol=5e-2)}
+_KEEP = []
+
+# a third configuration: recurrent layers only at first (no keys or values anywhere before layer 2), a convolution of
+# one tap, one kv head per head, a rotation of the whole head, no mask, a chunk of one position, top = experts = 1
+ODD = {
+    "architecture": "Vunepel", "vocab": 67, "width": 72, "norm": {"eps": 1e-4},
+    "layers": [
+        {"type": "channel_delta", "mlp": {"kind": "moe", "router": {"experts": 1, "top": 1, "scale": 0.7}, "expert": {"ff": 16, "limit": 1.5}},
+         "mixer": {"heads": 3, "kv_heads": 3, "dim": 12, "vdim": 20, "conv": 1, "ranks": {"decay": 1, "gate": 2}}},
+        {"type": "channel_delta", "mlp": None,
+         "mixer": {"heads": 2, "kv_heads": 1, "dim": 36, "vdim": 8, "conv": 7, "ranks": {"decay": 9, "gate": 1}}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 40, "limit": 0.8},
+         "mixer": {"heads": 1, "kv_heads": 1, "dim": 10, "vdim": 6, "scale": 0.4, "diff": 0.0, "rot": {"dims": 10, "base": 100.0}}},
+        {"type": "attention", "mlp": {"kind": "moe", "router": {"experts": 7, "top": 3, "scale": 1.0}, "expert": {"ff": 9, "limit": 5.0},
+                                      "shared": {"ff": 11, "limit": 0.5}},
+         "mixer": {"heads": 1, "kv_heads": 1, "dim": 10, "vdim": 6, "scale": 0.9, "diff": 0.6, "rot": {"dims": 10, "base": 100.0},
+                   "mask": {"size": 1}, "kv_from": 2}},
+        {"type": "attention", "mlp": None,
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 20, "vdim": 130, "scale": 0.2, "diff": 0.25, "mask": {"size": 65}}},
+    ],
+}
+MODELS = ("vunepel-tiny-a", "vunepel-tiny-b", "odd")
+CASES = [(name, dtype) for name in MODELS for dtype in DTYPES]
+
+
+def close(actual, expected, dtype, what="", model_rows=False):
+    """``model_rows``: logits of a whole model.  In bfloat16 a router's close call may fall the other way than in the
+    oracle (the normed rows differ by their rounding) and changes that one position's logits; up to one position in a
+    hundred (at least one) may therefore be off.  The float32 twin of every such test holds every position."""
+    actual, expected = actual.float().cpu(), expected.float().cpu()
+    assert actual.shape == expected.shape, f"{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}"
+    tol = TOL[dtype]
+    bad = ~((actual - expected).abs() <= tol["atol"] + tol["rtol"] * expected.abs())
+    if bad.any():
+        rows = bad.reshape(bad.shape[0], -1).any(dim=1).nonzero().flatten().tolist()
+        if model_rows and dtype == "bf16" and len(rows) <= max(1, bad.shape[0] // 100):
+            return
+        raise AssertionError(f"{what}: {int(bad.sum())} values differ, first wrong row {rows[0]} of {bad.shape[0]} "
+                             f"(wrong rows {rows[:12]}), max abs error {float((actual - expected).abs().max()):.3e}")
+
+
+# ----------------------------------------------------------------------------- models and their oracle
+def config_of(name):
+    return config_from_dict(ODD) if name == "odd" else load_preset(name)
+
+
+@functools.lru_cache(maxsize=None)
+def model(name: str, dtype: str, peaky: bool = False):
+    """(folder, raw config, float weights for the oracle).  ``peaky``: the q and k norm weights of the attention
+    layers are three times as large, so that few keys, far ones among them, carry each softmax."""
+    config = config_of(name)
+    holder = tempfile.TemporaryDirectory(prefix=f"qt_{name}_{dtype}_")
+    _KEEP.append(holder)
+    folder = write_random_model(holder.name, config, seed=5 + len(name), dtype=STORE[dtype])
+    if peaky:
+        checkpoint = Checkpoint(folder)
+        tensors = {n: checkpoint.read(n) for n in checkpoint.names()}
+        for n in list(tensors):
+            if n.endswith((".mix.q.norm", ".mix.k.norm")):
+                tensors[n] = (tensors[n].float() * 3.0).to(tensors[n].dtype)
+        write_safetensors(Path(folder) / "model.safetensors", tensors)
+    checkpoint = Checkpoint(folder)
+    weights = {n: checkpoint.read(n).float() for n in checkpoint.names()}
+    return folder, config.to_hf_dict(), weights
+
+
+@functools.lru_cache(maxsize=None)
+def oracle(name: str, dtype: str, peaky: bool, tokens: tuple) -> torch.Tensor:
+    _, raw, weights = model(name, dtype, peaky)
+    return plain.forward(raw, weights, list(tokens), torch.float64).float()
+
+
+def tokens_of(name: str, length: int, seed: int) -> list[int]:
+    generator = torch.Generator().manual_seed(77 + seed)
+    return torch.randint(0, config_of(name).vocab_size, (length,), generator=generator).tolist()
+
+
+def engine_of(name, dtype, peaky=False, **kwargs) -> Engine:
+    kwargs.setdefault("max_tokens", 2048)
+    return Engine.from_pretrained(model(name, dtype, peaky)[0], dtype=dtype, **kwargs)
+
+
+# ----------------------------------------------------------------------------- each mechanism alone
+@pytest.mark.parametrize("width, rows", [(96, 5), (130, 33), (7, 1)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_dynamic_tanh_folds_two_additions(width, rows, out_dtype):
+    torch.manual_seed(width)
+    stream = torch.randn(rows, width, device=DEV)
+    first = torch.randn(3, rows, width, device=DEV)              # split sums
+    second = torch.randn(1, rows, width, device=DEV)
+    weight, bias, alpha = torch.randn(width, device=DEV), torch.randn(width, device=DEV), 0.37
+    want_stream = stream + first.sum(0) + second[0]
+    want = plain.dynamic_tanh(want_stream.double(), weight.double(), bias.double(), alpha).float()
+    # listed rows: the stream stays as it is
+    listed = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out = torch.empty(2, width, dtype=out_dtype, device=DEV)
+    before = stream.clone()
+    kernels.add_dyt(stream, [GemmOut(first), GemmOut(second)], weight, bias, alpha, out, listed)
+    assert torch.equal(stream, before)
+    torch.testing.assert_close(out.float(), want[listed.long()].to(out_dtype).float(), atol=1e-5 if out_dtype == torch.float32 else 2e-2, rtol=1e-5 if out_dtype == torch.float32 else 2e-2)
+    out = torch.empty(rows, width, dtype=out_dtype, device=DEV)
+    kernels.add_dyt(stream, [GemmOut(first), GemmOut(second)], weight, bias, alpha, out)
+    torch.testing.assert_close(stream, want_stream, atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(out.float(), want.float(), atol=1e-5 if out_dtype == torch.float32 else 2e-2, rtol=1e-5 if out_dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens, inter, limit", [(3, 40, 2.0), (300, 72, 0.5), (17, 13, 7.0)])
+def test_capped_gate(dtype, tokens, inter, limit):
+    torch.manual_seed(inter)
+    gate_up = (torch.randn(2, tokens, 2 * inter, device=DEV) * 3.0)
+    out = torch.empty(tokens, inter, dtype=STORE[dtype], device=DEV)
+    kernels.swiglu(GemmOut(gate_up), out, 0, kernels.CAPPED_GATE, limit)
+    total = gate_up.sum(0).double()
+    want = plain.clamped_gate(total[:, :inter], total[:, inter:], limit)
+    assert float(want.abs().max()) <= limit * (limit + 1) + 1e-6
+    close(out, want, dtype, "capped gate")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, dv, lam", [(3, 20, 0.7), (1, 130, -0.4), (8, 64, 0.05)])
+def test_two_maps_into_one_head(dtype, heads, dv, lam):
+    torch.manual_seed(dv)
+    tokens, eps, post = 9, 1e-5, 0.6
+    ctx = torch.randn(tokens, 2 * heads, dv, device=DEV).to(STORE[dtype])
+    out = torch.empty(tokens, heads, dv, dtype=STORE[dtype], device=DEV)
+    kernels.map_difference(ctx, out, lam, eps, post)
+    maps = ctx.double()
+    want = plain.rms_unit(maps[:, :heads] - lam * maps[:, heads:], eps) * post
+    close(out, want, dtype, "difference of the maps")
+
+
+def paged(values: torch.Tensor, page_tokens: int, order: list[int], dtype):
+    """values [T, heads, d] into a pool [pages, heads, page_tokens, d] whose pages are used in ``order``; unused room
+    holds large numbers."""
+    tokens, heads, d = values.shape
+    pool = torch.full((len(order) + 2, heads, page_tokens, d), 50.0, dtype=dtype, device=DEV)
+    for t in range(tokens):
+        pool[order[t // page_tokens], :, t % page_tokens] = values[t].to(dtype)
+    return pool
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, d, dv, chunk", [(4, 2, 16, 32, 21), (3, 3, 40, 8, None), (2, 1, 24, 130, 64), (1, 1, 8, 8, 1),
+                                                              (4, 2, 64, 64, 100), (2, 1, 32, 32, 21), (2, 2, 128, 128, 70), (17, 1, 48, 48, 64)])
+def test_attention_in_chunks_over_shared_values(dtype, heads, kv_heads, d, dv, chunk):
+    """Two maps per head as the kernels see them (map-major heads; values with kv_heads heads for 2 * kv_heads key
+    heads), a prompt of 150 tokens and then one token per step.  In every map one key carries the softmax of the
+    queries behind it: the first key of the query's own chunk for even heads (just inside), and for odd heads the last
+    key of the chunk before (just outside: it must not be seen).  Values as wide as the keys in steps of 16 take the
+    tensor-core kernels in bfloat16 (head sizes 64 and 128 the tcgen05 prefill kernel), everything else the generic ones."""
+    torch.manual_seed(d + dv)
+    total, prompt, page = 160, 150, 64
+    nq, nkv = 2 * heads, 2 * kv_heads
+    store = STORE[dtype]
+    q = torch.randn(total, nq, d).to(store).float()
+    k = torch.randn(total, nkv, d).to(store).float()
+    v = torch.randn(total, kv_heads, dv).to(store).float()
+    size = chunk or 10 ** 6
+    for t in range(total):
+        start = t // size * size
+        for h in range(nq):
+            target = start if h % 2 == 0 else max(start - 1, 0)
+            kh = h // (nq // nkv)
+            q[t, h] = (q[t, h] + 6.0 * k[target, kh] / k[target, kh].norm()).to(store).float()
+    scale = 1.0 / math.sqrt(d)
+    place = torch.arange(total)
+    visible = (place[None, :] <= place[:, None]) & ((place[None, :] // size) == (place[:, None] // size))
+    want = torch.zeros(total, nq, dv, dtype=torch.float64)
+    for h in range(nq):
+        kh = h // (nq // nkv)
+        score = (q[:, h].double() @ k[:, kh].double().T) * scale
+        want[:, h] = torch.softmax(score.masked_fill(~visible, -math.inf), dim=-1) @ v[:, kh % kv_heads].double()
+    order = [3, 0, 2]
+    k_pool, v_pool = paged(k, page, order, store), paged(v, page, order, store)
+    table = torch.tensor([order + [0]], dtype=torch.int32, device=DEV)
+    out = torch.empty(prompt, nq, dv, dtype=store, device=DEV)
+    kernels.attention_prefill(q[:prompt].to(DEV, store), k_pool, v_pool, out, table, torch.tensor([0, prompt], dtype=torch.int32, device=DEV),
+                              torch.tensor([0], dtype=torch.int32, device=DEV), prompt, nkv, page, 0, None, scale, chunk=chunk)
+    close(out, want[:prompt], dtype, "prompt")
+    # a later portion of the prompt, from the cache
+    out = torch.empty(prompt - 100, nq, dv, dtype=store, device=DEV)
+    kernels.attention_prefill(q[100:prompt].to(DEV, store), k_pool, v_pool, out, table, torch.tensor([0, prompt - 100], dtype=torch.int32, device=DEV),
+                              torch.tensor([100], dtype=torch.int32, device=DEV), prompt - 100, nkv, page, 0, None, scale, chunk=chunk)
+    close(out, want[100:prompt], dtype, "portion")
+    for t in range(prompt, total):
+        for splits in (1, 2):
+            out = torch.empty(1, nq, dv, dtype=store, device=DEV)
+            kernels.attention_decode(q[t:t + 1].to(DEV, store), k_pool, v_pool, out, table, torch.tensor([t + 1], dtype=torch.int32, device=DEV),
+                                     nkv, page, 0, None, scale, splits, torch.empty(4 * nq * dv, device=DEV), torch.empty(8 * nq, device=DEV), chunk=chunk)
+            close(out, want[t:t + 1], dtype, f"token {t}, {splits} ranges")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq, nkv, nv, d, dv, rotary", [(4, 2, 1, 16, 24, 8), (2, 2, 1, 10, 6, 10), (6, 2, 2, 32, 32, 0), (2, 2, 2, 8, 8, 4)])
+def test_norm_rotation_and_cache_write_with_values_of_their_own_shape(dtype, nq, nkv, nv, d, dv, rotary):
+    torch.manual_seed(d)
+    store = STORE[dtype]
+    tokens, page, eps = 70, 64, 1e-5
+    width = (nq + nkv) * d + nv * dv
+    proj = torch.randn(2, tokens, width, device=DEV)
+    q_w, k_w = torch.rand(d, device=DEV) + 0.5, torch.rand(d, device=DEV) + 0.5
+    positions = torch.arange(5, 5 + tokens)
+    cos_sin = None
+    if rotary:
+        freq = 100.0 ** (-2.0 * torch.arange(rotary // 2, dtype=torch.float64) / rotary)
+        angle = torch.arange(200, dtype=torch.float64)[:, None] * freq[None, :]
+        cos_sin = torch.cat((angle.cos(), angle.sin()), dim=-1).float().to(DEV)
+    q_out = torch.empty(tokens, nq, d, dtype=store, device=DEV)
+    k_pool = torch.zeros(3, nkv, page, d, dtype=store, device=DEV)
+    v_pool = torch.zeros(3, nv, page, dv, dtype=store, device=DEV)
+    table = torch.tensor([[2, 0, 1]], dtype=torch.int32, device=DEV)
+    kernels.qk_norm_rope_write(GemmOut(proj), q_out, k_pool, v_pool, torch.zeros(tokens, dtype=torch.int32, device=DEV),
+                               positions.to(DEV, torch.int32), table, q_w, k_w, eps, cos_sin, nq, nkv, d, page, 0,
+                               v_heads=nv, v_head_dim=dv)
+    total = proj.sum(0).double().cpu()
+    q = plain.rms_unit(total[:, :nq * d].view(tokens, nq, d), eps) * q_w.double().cpu()
+    k = plain.rms_unit(total[:, nq * d:(nq + nkv) * d].view(tokens, nkv, d), eps) * k_w.double().cpu()
+    if rotary:
+        q, k = plain.rotate(q, positions, rotary, 100.0), plain.rotate(k, positions, rotary, 100.0)
+    v = total[:, (nq + nkv) * d:].view(tokens, nv, dv)
+    close(q_out, q, dtype, "q")
+    for t in (0, 58, 59, 69):
+        p = int(positions[t])
+        close(k_pool[int(table[0, p // page]), :, p % page], k[t], dtype, f"k of token {t}")
+        close(v_pool[int(table[0, p // page]), :, p % page], v[t], dtype, f"v of token {t}")
+
+
+class _Step:
+    """The fields of a step that the recurrent kernels read."""
+
+    def __init__(self, lengths, past, slots):
+        starts = [0]
+        for n in lengths:
+            starts.append(starts[-1] + n)
+        as_int = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)
+        self.n_seqs = len(lengths)
+        self.seq_start, self.seq_past, self.slots = as_int(starts), as_int(past), as_int(slots)
+        self.token_seq = as_int([s for s, n in enumerate(lengths) for _ in range(n)])
+        self.token_pos = as_int([past[s] + i for s, n in enumerate(lengths) for i in range(n)])
+
+
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, taps", [(2, 1, 16, 32, 4), (3, 3, 12, 20, 1), (4, 2, 36, 8, 7), (1, 1, 72, 136, 2), (2, 2, 130, 40, 3)])
+def test_delta_rule_kernels_in_portions_of_two_sequences(heads, kv_heads, dim, vdim, taps):
+    """Projection output -> convolution, SiLU, unit norms, decays, recurrence, gated head norm, for two sequences whose
+    tokens arrive in unequal portions (one of a single token), the states and the convolutions' last inputs carried
+    in slots that are not in order; against the plain mixer on the whole sequences."""
+    torch.manual_seed(dim * vdim)
+    width, ra, rg, eps = 24, 5, 3, 1e-5
+    lengths = (41, 23)
+    names = {"q": (kv_heads * dim, width), "k": (kv_heads * dim, width), "v": (heads * vdim, width), "b": (heads, width), "a1": (ra, width),
+             "g1": (rg, width), "a2": (heads * dim, ra), "g2": (heads * vdim, rg), "o": (width, heads * vdim)}
+    tensors = {f"m.{n}": torch.randn(shape) * (0.5 if n in ("a2", "g2") else 0.4) for n, shape in names.items()}
+    tensors["m.dt_bias"] = torch.randn(heads * dim) - 2.0
+    tensors["m.A_log"] = torch.randn(heads) * 0.3
+    tensors["m.norm"] = torch.rand(vdim) + 0.5
+    tensors["m.o"] = torch.eye(heads * vdim)[:width] if heads * vdim >= width else torch.randn(width, heads * vdim)
+    for n, channels in (("q", kv_heads * dim), ("k", kv_heads * dim), ("v", heads * vdim)):
+        tensors[f"m.{n}.conv"] = torch.randn(channels, taps) * 0.5 if taps > 1 else torch.ones(channels, 1)
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim}
+    hs = [torch.randn(n, width, dtype=torch.float64) for n in lengths]
+    channels = 2 * kv_heads * dim + heads * vdim
+    first = torch.cat([tensors[f"m.{n}"] for n in ("q", "k", "v", "b", "a1", "g1")], dim=0).double()
+    conv = torch.cat([tensors[f"m.{n}.conv"] for n in ("q", "k", "v")], dim=0).float().to(DEV)
+    slots = [3, 1]
+    states = torch.zeros(5, heads, dim, vdim, device=DEV)
+    kept = torch.zeros(5, max(taps - 1, 1), channels, device=DEV)
+    got = [[], []]
+    done = [0, 0]
+    for portion in ((17, 1), (1, 2), (2, 20), (21, 0)):
+        live = [s for s in (0, 1) if portion[s]]
+        step = _Step([portion[s] for s in live], [done[s] for s in live], [slots[s] for s in live])
+        rows = torch.cat([hs[s][done[s]:done[s] + portion[s]] for s in live], dim=0)
+        tokens = rows.shape[0]
+        proj = GemmOut(torch.stack(((rows @ first.T) * 0.25, (rows @ first.T) * 0.75)).float().to(DEV).contiguous())
+        q = torch.empty(tokens, kv_heads, dim, device=DEV)
+        k = torch.empty_like(q)
+        v = torch.empty(tokens, heads, vdim, device=DEV)
+        beta = torch.empty(tokens, heads, device=DEV)
+        kernels.delta_prepare(proj, conv, kept if taps > 1 else kept[:, :0], step, q, k, v, beta, heads, kv_heads, dim, vdim, 1e-6)
+        decay = torch.empty(tokens, heads, dim, device=DEV)
+        gate = torch.empty(tokens, heads, vdim, device=DEV)
+        kernels.lowrank(proj, channels + heads, tensors["m.a2"].t().contiguous().to(DEV), decay.view(tokens, -1), tensors["m.dt_bias"].to(DEV),
+                        tensors["m.A_log"].to(DEV), dim)
+        kernels.lowrank(proj, channels + heads + ra, tensors["m.g2"].t().contiguous().to(DEV), gate.view(tokens, -1))
+        read = torch.empty(tokens, heads, vdim, device=DEV)
+        kernels.delta_scan(q, k, v, beta, decay, states, read, step)
+        out = torch.empty(tokens, heads, vdim, device=DEV)
+        kernels.gated_head_norm(read, gate, tensors["m.norm"].to(DEV), eps, out)
+        at = 0
+        for s in live:
+            got[s].append(out[at:at + portion[s]].cpu())
+            at += portion[s]
+            done[s] += portion[s]
+    assert float(states[[0, 2, 4]].abs().max()) == 0.0 and float(kept[[0, 2, 4]].abs().max()) == 0.0
+    tensors["m.o"] = torch.eye(heads * vdim)
+    for s in (0, 1):
+        want = plain.channel_delta(hs[s], tensors, "m", mixer, eps)
+        torch.testing.assert_close(torch.cat(got[s]).reshape(lengths[s], -1), want.float(), atol=2e-4, rtol=2e-4)
+
+
+def test_delta_rule_state_keeps_a_far_write():
+    """One strong write at the first token, decays of nearly one, 600 tokens of small writes, and a query along the
+    first key: what is read at the end is mostly the first token's value."""
+    heads, dim, vdim, tokens = 1, 16, 8, 600
+    torch.manual_seed(1)
+    k = torch.nn.functional.normalize(torch.randn(tokens, 1, dim), dim=-1)
+    q = k[0:1].expand(tokens, 1, dim).contiguous()
+    v = torch.randn(tokens, heads, vdim) * 0.01
+    v[0] = torch.arange(1.0, vdim + 1.0)
+    beta = torch.full((tokens, heads), 0.02)
+    beta[0] = 1.0
+    decay = torch.full((tokens, heads, dim), 0.9999)
+    state = torch.zeros(2, heads, dim, vdim, device=DEV)
+    read = torch.empty(tokens, heads, vdim, device=DEV)
+    kernels.delta_scan(q.to(DEV), k.to(DEV), v.to(DEV), beta.to(DEV), decay.to(DEV), state, read, _Step([tokens], [0], [0]))
+    s = torch.zeros(dim, vdim, dtype=torch.float64)
+    for t in range(tokens):
+        s = s * decay[t, 0].double()[:, None]
+        u = beta[t, 0].double() * (v[t, 0].double() - s.T @ k[t, 0].double())
+        s = s + k[t, 0].double()[:, None] * u[None, :]
+    torch.testing.assert_close(read[-1, 0].cpu(), (s.T @ q[-1, 0].double()).float(), atol=1e-4, rtol=1e-4)
+    assert float(read[-1, 0, -1]) > 0.5 * vdim * 0.5          # the first value is still most of what is read
+    torch.testing.assert_close(state[0, 0].cpu(), s.float(), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens, experts, top, width, ff, shared", [(5, 3, 1, 40, 24, 16), (33, 4, 4, 64, 72, 0), (300, 12, 2, 128, 96, 64),
+                                                                     (700, 5, 3, 72, 200, 8), (9, 40, 6, 24, 10, 0)])
+def test_routed_experts_against_the_plain_router(dtype, tokens, experts, top, width, ff, shared):
+    from qwen_triton_b200.parts.base import Runtime, Workspace
+    from qwen_triton_b200.parts.feed_forward import RoutedExperts
+    torch.manual_seed(tokens + experts)
+    store = STORE[dtype]
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 1.7}, "expert": {"ff": ff, "limit": 1.2},
+           "shared": {"ff": shared, "limit": 0.9} if shared else None}
+    tensors = {"f.router": torch.randn(experts, width) * 0.5}
+    for e in range(experts):
+        tensors[f"f.e{e}.gate"], tensors[f"f.e{e}.up"] = torch.randn(ff, width) * 0.3, torch.randn(ff, width) * 0.3
+        tensors[f"f.e{e}.down"] = torch.randn(width, ff) * 0.3
+    if shared:
+        tensors["f.shared.gate"], tensors["f.shared.up"] = torch.randn(shared, width) * 0.3, torch.randn(shared, width) * 0.3
+        tensors["f.shared.down"], tensors["f.shared.sg"] = torch.randn(width, shared) * 0.3, torch.randn(1, width) * 0.3
+    tensors = {n: t.to(store).float() for n, t in tensors.items()}
+    workspace = Workspace(torch.device(DEV))
+    runtime = Runtime(device=torch.device(DEV), dtype=store, max_step_tokens=tokens, max_positions=64, workspace=workspace)
+    part = RoutedExperts({"hidden_size": width, "expert_size": ff, "experts": experts, "top": top, "route_scale": 1.7,
+                          "activation": kernels.CAPPED_GATE, "limit": 1.2, "shared": {"intermediate_size": shared, "limit": 0.9} if shared else None,
+                          "expert": "e{}", "shared_gate": "sg", "weight_suffix": ""}, "f", runtime)
+    part.load(lambda name: tensors[name])
+    workspace.allocate()
+    x = torch.randn(tokens, width).to(store)
+    got = part.forward(x.to(DEV), None).value()
+    want = plain.routed_ff(x.double(), tensors, "f", mlp)
+    # the router's sums are float in both types (its operands' products are exact), so only a tie to within float
+    # rounding may fall either way: leave out rows whose choice is that narrow
+    scores = torch.sigmoid(x.double() @ tensors["f.router"].double().T).sort(dim=-1, descending=True).values
+    clear = torch.ones(tokens, dtype=torch.bool) if top == experts else (scores[:, top - 1] - scores[:, top]) > 1e-5
+    assert int(clear.sum()) >= tokens - 2
+    close(got.cpu()[clear], want[clear], dtype, "routed experts")
+
+
+# ----------------------------------------------------------------------------- whole models
+def run_whole(engine, tokens):
+    slot = engine.new_sequence()
+    try:
+        return engine.step([StepEntry(slot, list(tokens), list(range(len(tokens))))]).cpu()
+    finally:
+        engine.release(slot)
+
+
+@pytest.mark.parametrize("name, dtype", CASES)
+def test_each_request_alone_and_whole(name, dtype):
+    engine = engine_of(name, dtype, peaky=True)
+    for length, seed in ((1, 0), (2, 1), (7, 2), (150, 3)):
+        tokens = tokens_of(name, length, seed)
+        close(run_whole(engine, tokens), oracle(name, dtype, True, tuple(tokens)), dtype, f"{name} {length} tokens", model_rows=True)
+    engine.check_kernels()
+
+
+@pytest.mark.parametrize("name, dtype", CASES)
+def test_prompt_then_token_by_token_across_chunk_and_page_edges(name, dtype):
+    """A prompt that ends just before a page's edge and inside a chunk, then 75 tokens one by one: they cross the page
+    edges at 64 and 128 and the edges of the presets' chunks (33, 65, 70, 128), in captured steps from the second on."""
+    engine = engine_of(name, dtype, peaky=True)
+    tokens = tokens_of(name, 135, 4)
+    want = oracle(name, dtype, True, tuple(tokens))
+    slot = engine.new_sequence()
+    got = [engine.step([StepEntry(slot, tokens[:60], list(range(60)))]).cpu()]
+    for t in range(60, len(tokens)):
+        got.append(engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu())
+    engine.release(slot)
+    close(torch.cat(got), want, dtype, f"{name} token by token", model_rows=True)
+    assert engine.graph_replays > 0
+    engine.check_kernels()
+
+
+@pytest.mark.parametrize("name, dtype", CASES)
+@pytest.mark.parametrize("portion", [2, 3, 17, 64, 100])
+def test_portions_of_a_prompt(name, dtype, portion):
+    engine = engine_of(name, dtype, peaky=True)
+    tokens = tokens_of(name, 141, 5)
+    want = oracle(name, dtype, True, tuple(tokens))
+    slot = engine.new_sequence()
+    got = []
+    for begin in range(0, len(tokens), portion):
+        piece = tokens[begin:begin + portion]
+        got.append(engine.step([StepEntry(slot, piece, list(range(len(piece))))]).cpu())
+    engine.release(slot)
+    close(torch.cat(got), want, dtype, f"{name} in portions of {portion}", model_rows=True)
+
+
+@pytest.mark.parametrize("name, dtype", CASES)
+def test_passes_smaller_than_a_prompt(name, dtype):
+    """A step whose tokens do not fit one pass is cut inside the engine; states and kept inputs go from pass to pass."""
+    engine = engine_of(name, dtype, peaky=True, max_step_tokens=48)
+    tokens = tokens_of(name, 130, 6)
+    close(run_whole(engine, tokens), oracle(name, dtype, True, tuple(tokens)), dtype, f"{name} in passes of 48", model_rows=True)
+
+
+@pytest.mark.parametrize("name, dtype", CASES)
+def test_unequal_batches_with_slots_and_pages_used_again(name, dtype):
+    """Three rounds on one engine.  Each: unequal prompts in one batch (one of a single token), then decoded together
+    while the shorter requests end earlier; the slots, state rows and pages of a round are used again by the next."""
+    engine = engine_of(name, dtype, peaky=True, max_tokens=640)
+    for round_ in range(3):
+        lengths = [(1, 5), (70, 9), (33, 2), (129, 12)][round_ % 2:][:3]
+        requests = [tokens_of(name, prompt + decoded, 10 * round_ + i) for i, (prompt, decoded) in enumerate(lengths)]
+        slots = [engine.new_sequence() for _ in requests]
+        got = [[] for _ in requests]
+        logits = engine.step([StepEntry(slot, req[:prompt], list(range(prompt))) for slot, req, (prompt, _) in zip(slots, requests, lengths)]).cpu()
+        at = 0
+        for i, (prompt, _) in enumerate(lengths):
+            got[i].append(logits[at:at + prompt])
+            at += prompt
+        for step in range(max(d for _, d in lengths)):
+            live = [i for i, (_, d) in enumerate(lengths) if step < d]
+            logits = engine.step([StepEntry(slots[i], [requests[i][lengths[i][0] + step]], [0]) for i in live]).cpu()
+            for row, i in enumerate(live):
+                got[i].append(logits[row:row + 1])
+            for i, (_, d) in enumerate(lengths):
+                if step == d - 1:
+                    engine.release(slots[i])
+        for i, req in enumerate(requests):
+            close(torch.cat(got[i]), oracle(name, dtype, True, tuple(req)), dtype, f"{name} round {round_} request {i}", model_rows=True)
+    engine.check_kernels()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_of_several_rows(dtype):
+    """Five rows decoded for 150 steps from short prompts: every chunk edge of the model is crossed several times and the
+    recurrent states run on for the whole length."""
+    name = "vunepel-tiny-a"
+    engine = engine_of(name, dtype, peaky=True)
+    requests = [tokens_of(name, 3 + 2 * i + 150, 40 + i) for i in range(5)]
+    slots = [engine.new_sequence() for _ in requests]
+    engine.step([StepEntry(slot, req[:3 + 2 * i], []) for i, (slot, req) in enumerate(zip(slots, requests))])
+    last = None
+    for step in range(150):
+        last = engine.step([StepEntry(slot, [req[3 + 2 * i + step]], [0]) for i, (slot, req) in enumerate(zip(slots, requests))]).cpu()
+    for i, req in enumerate(requests):
+        close(last[i:i + 1], oracle(name, dtype, True, tuple(req))[-1:], dtype, f"row {i} after 150 steps", model_rows=True)
+    engine.check_kernels()
+
+
+@pytest.mark.parametrize("name", MODELS)
+def test_greedy_generation_through_the_entry_point(name):
+    folder, _, _ = model(name, "fp32")
+    lm = QwenB200ForCausalLM.from_pretrained_hf(folder, dtype="fp32", max_tokens=1024)
+    prompts = [tokens_of(name, n, 60 + n) for n in (5, 1, 40)]
+    results = lm.generate(prompts, max_new_tokens=12, ignore_eos=True)
+    for prompt, result in zip(prompts, results):
+        assert len(result.tokens) == 12
+        sequence = list(prompt)
+        for token in result.tokens:
+            logits = oracle(name, "fp32", False, tuple(sequence))[-1]
+            best = logits.topk(2).values
+            if float(best[0] - best[1]) > 1e-3:          # a clear choice: the library must have made it
+                assert int(logits.argmax()) == token, f"{name}: after {len(sequence)} tokens"
+            sequence.append(token)
+    # the same in bfloat16 with temperature runs and stays within the vocabulary
+    lm16 = QwenB200ForCausalLM.from_pretrained_hf(model(name, "bf16")[0], dtype="bf16", max_tokens=1024)
+    for result in lm16.generate(prompts, max_new_tokens=12, ignore_eos=True, temperature=0.7, seed=3):
+        assert len(result.tokens) == 12 and all(0 <= t < config_of(name).vocab_size for t in result.tokens)
+
+
+def test_random_weights_on_the_device_equal_the_written_folder():
+    name = "vunepel-tiny-b"
+    folder, _, _ = model(name, "bf16")
+    tokens = tokens_of(name, 50, 70)
+    written = run_whole(Engine.from_pretrained(folder, dtype="bf16", max_tokens=512), tokens)
+    drawn = run_whole(Engine.from_config(config_of(name), seed=5 + len(name), dtype="bf16", max_tokens=512), tokens)
+    assert torch.equal(written, drawn)
+
+
+def test_sizes_that_only_the_tensors_give():
+    """A folder's config.json without the narrow projections' column counts: they are read from the tensors' shapes."""
+    folder, raw, _ = model("vunepel-tiny-a", "fp32")
+    with tempfile.TemporaryDirectory() as tmp:
+        bare = json.loads(json.dumps(raw))
+        for layer in bare["layers"]:
+            layer["mixer"].pop("ranks", None)
+        (Path(tmp) / "config.json").write_text(json.dumps(bare))
+        os.symlink(Path(folder) / "model.safetensors", Path(tmp) / "model.safetensors")
+        tokens = tokens_of("vunepel-tiny-a", 20, 80)
+        close(run_whole(Engine.from_pretrained(tmp, dtype="fp32", max_tokens=256), tokens), oracle("vunepel-tiny-a", "fp32", False, tuple(tokens)), "fp32")
+
+
+def test_command_line_with_a_preset_and_random_weights():
+    result = subprocess.run([sys.executable, "-m", "qwen_triton_b200.scripts.smoke", "--preset", "vunepel-tiny-a", "--random-weights",
+                             "--random-prompts", "9,2", "--max-new-tokens", "5", "--dtype", "bf16"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert result.returncode == 0, result.stderr[-2000:]
+
+
+@pytest.mark.parametrize("dtype, name", [("float32", "fp32"), ("bfloat16", "bf16")])
+def test_trace_replay_of_a_folder(tmp_path, dtype, name):
+    """bin/trace_run as a child process: two requests start together, decode together, one ends earlier; a third
+    comes alone afterwards and finds their slots."""
+    model_name = "vunepel-tiny-b"
+    folder, _, _ = model(model_name, name)
+    a, b, c = tokens_of(model_name, 90, 90), tokens_of(model_name, 31, 91), tokens_of(model_name, 70, 92)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:80], "want": [0, 63, 64, 79]}, {"id": "b", "tokens": b[:30], "want": [29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [a[80]], "want": [0]}, {"id": "b", "tokens": [b[30]], "want": [0]}], "end": ["b"]}]
+    for i in range(81, 90):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [a[i]], "want": [0] if i % 2 else []}], "end": ["a"] if i == 89 else []})
+    steps.append({"step": len(steps), "entries": [{"id": "c", "tokens": c, "want": [69]}], "end": ["c"]})
+    out = tmp_path / "out"
+    result = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out), "--max-tokens", "160"],
+                            input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert result.returncode == 0, result.stderr[-2000:]
+    assert [line for line in result.stdout.splitlines() if line.startswith("done")] == [f"done {i}" for i in range(len(steps))]
+    want = {"a": oracle(model_name, name, False, tuple(a)), "b": oracle(model_name, name, False, tuple(b)), "c": oracle(model_name, name, False, tuple(c))}
+    at = {"a": 0, "b": 0, "c": 0}
+    import numpy as np
+    for record in steps:
+        rows = []
+        for entry in record["entries"]:
+            rows += [want[entry["id"]][at[entry["id"]] + w] for w in entry["want"]]
+            at[entry["id"]] += len(entry["tokens"])
+        path = out / f"{record['step']}.f32"
+        if not rows:
+            assert not path.exists()
+            continue
+        got = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(len(rows), -1).copy())
+        close(got, torch.stack(rows), name, f"step {record['step']}", model_rows=True)
