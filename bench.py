@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the Qwen3-8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl b200|reference] [--temperature T]
-    python bench.py --workload 0.6b-unequal | 32b-long | lederax-layers
+    python bench.py --workload 0.6b-unequal | 32b-long | lederax-layers | vunepel-layers
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from a 2,048-token cache,
 timed on the device over the decode steps (step function plus greedy sampling kernel, tokens given
@@ -19,7 +19,10 @@ lengths uniform in 64..2,048, 128 new tokens each, through ``generate``), ``32b-
 64 decoded from 2,048 to 4,096 positions, with the roofline fraction in windows of 64 steps near 2,048, 3,072 and 4,096),
 ``lederax-layers`` (four layers of the Lederax design at three sets of sizes that resemble a real model's, beside a Qwen3
 dense model of the same width, heads, window and as many weights read per token: prefill of one prompt and one-token steps
-at batch 8 and 64, each with its share of the measured peaks).
+at batch 8 and 64, each with its share of the measured peaks), ``vunepel-layers`` (the same for four layers of the
+Vunepel design: differential attention with a dense feed-forward, two gated-delta-rule layers with routed experts, an
+attention layer that reads the first one's keys and values; ``--size``, ``--arm`` and ``--phase`` run one of its
+measurements alone, for a profiler).
 """
 from __future__ import annotations
 
@@ -53,7 +56,10 @@ def parse_args():
     parser.add_argument("--no-prefill", action="store_true")
     parser.add_argument("--min-seconds", type=float, default=2.0, help="a timed region lasts at least this long")
     parser.add_argument("--temperature", type=float, default=0.0, help="sampling temperature of the end-to-end run (0: greedy)")
-    parser.add_argument("--workload", default=None, choices=["0.6b-unequal", "32b-long", "lederax-layers"])
+    parser.add_argument("--workload", default=None, choices=["0.6b-unequal", "32b-long", "lederax-layers", "vunepel-layers"])
+    parser.add_argument("--size", default=None, help="vunepel-layers: only the size whose name starts with this")
+    parser.add_argument("--arm", default=None, choices=["vunepel", "dense"], help="vunepel-layers: only this model")
+    parser.add_argument("--phase", default=None, choices=["prefill", "decode8", "decode64"], help="vunepel-layers: only this measurement")
     return parser.parse_args()
 
 
@@ -217,6 +223,104 @@ def time_e2e(model, prompts, steps: int, warmup: int, min_seconds: float, most_s
     h2d = model.engine.last_meta_bytes + (8 * len(prompts) if temperature > 0 else 0)     # sampling keys: request and step per row
     run.close()
     return ms, h2d, 4 * len(prompts), steps
+
+
+VUNEPEL_SIZES = (
+    # name, width, attention heads (two score maps each), kv heads, map and value size, chunk, delta heads, delta kv heads, delta key size,
+    # delta value size, narrow columns, experts, top, expert width, shared width, dense width
+    ("w2048-h8x2x128-chunk1024-delta16x128-e16x1024-top2", 2048, 8, 2, 128, 1024, 16, 4, 128, 128, 64, 16, 2, 1024, 1024, 6144),
+    ("w4096-h16x2x128-chunk4096-delta32x128-e16x2048-top2", 4096, 16, 4, 128, 4096, 32, 8, 128, 128, 128, 16, 2, 2048, 2048, 12288),
+    ("w1024-h8x2x64-chunk512-delta8x64-e8x2048-top1", 1024, 8, 8, 64, 512, 8, 8, 64, 128, 32, 8, 1, 2048, 1024, 3072),
+)
+
+
+def run_vunepel_layers(args) -> dict:
+    """Prefill and one-token steps of four Vunepel layers at sizes that resemble a real model's (an attention layer
+    with a dense feed-forward, two delta-rule layers with routed experts and a shared expert, an attention layer that
+    reads the first one's keys and values, with routed experts), and of the Qwen3 dense layers that come closest: same
+    width and vocabulary, one head per score map with the same head size, a window as long as the chunk, and a gated
+    feed-forward that reads as many weights per token as the four layers' feed-forwards do on average."""
+    import torch
+
+    from qwen_triton_b200 import QwenB200ForCausalLM, config_from_dict
+
+    peak, peak_source = peaks()
+    vocab, prompt_len = 32768, args.prompt_len
+    out = []
+    for size in VUNEPEL_SIZES:
+        name, width, heads, kv_heads, dim, chunk, d_heads, d_kv, d_dim, d_vdim, rank, experts, top, ff, shared, dense_ff = size
+        if args.size and not name.startswith(args.size):
+            continue
+        moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.0}, "expert": {"ff": ff, "limit": 7.0},
+               "shared": {"ff": shared, "limit": 7.0}}
+        attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "diff": 0.3,
+                     "rot": {"dims": dim // 2, "base": 500000.0}, "mask": {"size": chunk}}
+        delta = {"heads": d_heads, "kv_heads": d_kv, "dim": d_dim, "vdim": d_vdim, "conv": 4, "ranks": {"decay": rank, "gate": rank}}
+        vunepel = {"architecture": "Vunepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+                   "layers": [{"type": "attention", "mixer": attention, "mlp": {"kind": "dense", "ff": dense_ff, "limit": 7.0}},
+                              {"type": "channel_delta", "mixer": delta, "mlp": moe},
+                              {"type": "channel_delta", "mixer": delta, "mlp": moe},
+                              {"type": "attention", "mixer": {**attention, "kv_from": 0}, "mlp": moe}]}
+        layers = 4
+        # weights a token multiplies with, per layer kind (the experts: the chosen ones and the shared one)
+        attn_own = width * (2 * heads + 2 * kv_heads) * dim + width * kv_heads * dim + heads * dim * width
+        attn_reader = width * 2 * heads * dim + heads * dim * width
+        delta_w = width * (2 * d_kv * d_dim + d_heads * d_vdim + d_heads + 2 * rank) + rank * d_heads * (d_dim + d_vdim) + d_heads * d_vdim * width
+        moe_token = 3 * width * (ff * top + shared) + width * (experts + 1)
+        mixers = attn_own + attn_reader + 2 * delta_w
+        token_weights = mixers + 3 * width * dense_ff + 3 * moe_token
+        inter = max(64, round((3 * width * dense_ff + 3 * moe_token) / 4 / (3 * width) / 64) * 64)
+        dense = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": vocab, "hidden_size": width,
+                 "intermediate_size": inter, "num_hidden_layers": layers, "num_attention_heads": 2 * heads,
+                 "num_key_value_heads": 2 * kv_heads, "head_dim": dim, "max_position_embeddings": 32768,
+                 "use_sliding_window": True, "sliding_window": chunk, "max_window_layers": 0}
+        dense_token = layers * (width * (2 * heads + 4 * kv_heads) * dim + 2 * heads * dim * width + 3 * width * inter)
+        entry = {"size": name, "layers": layers, "dense_intermediate": inter}
+        # keys a query sees on average: within its chunk (vunepel) or its window (dense)
+        seen = lambda context, span: min(context, span) / 2 if context <= span else span / 2
+
+        def moe_read(rows):
+            return 3 * width * (ff * min(experts, rows * top) + shared) + width * (experts + 1)
+
+        arms = (("vunepel", vunepel, token_weights, lambda rows: mixers + 3 * width * dense_ff + 3 * moe_read(rows),
+                 4 * 2 * 2 * heads * dim, 2 * (2 * 2 * kv_heads * dim + kv_heads * dim * 2), 2 * d_heads * d_dim * d_vdim * 4 * 2),
+                ("dense", dense, dense_token, lambda rows: dense_token, 4 * layers * 2 * heads * dim, layers * 2 * 2 * kv_heads * dim * 2, 0))
+        for label, raw, per_token, read_of, attn_flops_per_key, kv_bytes_per_key, state_bytes in arms:
+            if args.arm and label != args.arm:
+                continue
+            model = QwenB200ForCausalLM.from_config(config_from_dict(raw), seed=1, dtype="bf16",
+                                                    max_tokens=64 * (prompt_len + 512), max_seq_len=prompt_len + 512,
+                                                    max_step_tokens=max(4096, prompt_len), chunk_tokens=prompt_len)
+            result = {}
+            if args.phase in (None, "prefill"):
+                ms = time_prefill(model, prompt_len, vocab, repeats=args.steps if args.phase else 5, warmup=args.warmup if args.phase else 3)
+                keys = seen(prompt_len, chunk) if label == "vunepel" else min(chunk, prompt_len / 2)
+                flops = 2 * prompt_len * (per_token + vocab * width / prompt_len) + attn_flops_per_key * prompt_len * keys
+                result["prefill"] = {"tokens": prompt_len, "ms": round(ms, 3), "tokens_per_s": round(prompt_len * 1e3 / ms),
+                                     "tensor_fraction": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
+            for batch in (8, 64):
+                if args.phase not in (None, f"decode{batch}"):
+                    continue
+                prompts = random_prompts(batch, prompt_len, vocab, 300 + batch)
+                ms, launches, clocks, context, steps = time_decode(model, prompts, args.steps, args.warmup, vocab,
+                                                                   args.min_seconds / 4, 256)
+                keys = (context % chunk) if label == "vunepel" else min(chunk, context)
+                read = 2 * (read_of(batch) + vocab * width) + batch * (keys * kv_bytes_per_key + state_bytes)
+                result[f"decode_batch{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch * 1e3 / ms),
+                                                   "launches_per_step": round(launches / steps, 1), "steps": steps,
+                                                   "hbm_fraction": round(read / (ms * 1e-3) / (peak["hbm_gbs"] * 1e9), 4),
+                                                   "clocks": clocks}
+            entry[label] = result
+            print(f"[bench] {name} {label}: " + json.dumps({k: {a: b for a, b in v.items() if a != 'clocks'} for k, v in result.items()}),
+                  file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+        out.append(entry)
+    return {"workload": args.workload, "impl": "b200", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+            "config": {"prompt_len": prompt_len, "layers": 4, "vocab": vocab, "peaks": peak_source,
+                       "l2": "weights, caches and states of a step exceed L2 at every size but the smallest"},
+            "sizes": out}
+
 
 
 def time_prefill(model, tokens: int, vocab: int, repeats: int = 5, warmup: int = 3):
@@ -407,6 +511,8 @@ def run_workload(args) -> dict:
     """BASELINE's secondary workloads as they are stated."""
     if args.workload == "lederax-layers":
         return run_lederax_layers(args)
+    if args.workload == "vunepel-layers":
+        return run_vunepel_layers(args)
     import torch
 
     from qwen_triton_b200 import QwenB200ForCausalLM, StepEntry, load_preset

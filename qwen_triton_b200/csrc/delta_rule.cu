@@ -11,8 +11,11 @@
 //                          norms, beta = sigmoid(.)
 //   conv_keep_kernel       the last taps - 1 raw inputs of every sequence, kept for its next step
 //   lowrank_kernel         y = f(W2 (x) + bias) for a projection through a few columns (x is a slice of the first
-//                          projection's output): f = exp(-exp(rate_h) softplus(.)) for the decays, sigmoid for a gate
-//   delta_scan_kernel      the recurrence over the tokens of each sequence of the step (any count, one included)
+//                          projection's output): f = -exp(rate_h) softplus(.), the logarithm of the decays, or sigmoid for a gate
+//   delta_scan_kernel      the recurrence token by token (steps of few tokens per sequence: a state is read and written once
+//                          per token anyway)
+//   delta_chunk_prepare_kernel, delta_chunk_scan_kernel
+//                          the same recurrence in chunks of 16 tokens for longer steps (see there)
 //   gated_head_norm_kernel o / rms(o) * w * gate per head, into the element type of the output projection's input
 #include "common.cuh"
 
@@ -140,7 +143,7 @@ __global__ void __launch_bounds__(256) lowrank_kernel(const float* __restrict__ 
     for (int tt = 0; tt < LR_TOKENS; ++tt) {
         if (tt >= count) break;
         const float z = acc[tt] + b;
-        out[(size_t)(t0 + tt) * n_out + n] = MODE == LR_DECAY ? expf(-rate * softplusf(z)) : sigmoidf(z);
+        out[(size_t)(t0 + tt) * n_out + n] = MODE == LR_DECAY ? -rate * softplusf(z) : sigmoidf(z);     // the decay's logarithm
     }
 }
 
@@ -154,7 +157,7 @@ constexpr int SCAN_LANES = 8;
 constexpr int SCAN_CHUNK = 16;
 
 struct ScanParams {
-    const float* q; const float* k; const float* v; const float* beta; const float* decay;
+    const float* q; const float* k; const float* v; const float* beta; const float* decay;      // decay: logarithms, [T, heads, dim]
     float* state;                 // [slots + 1, heads, dim, vdim]
     float* out;                   // [T, heads, vdim]
     const int* seq_start; const int* slots;
@@ -226,7 +229,7 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) delta_scan_kernel(cons
                 const int i = sub + SCAN_LANES * m;
                 const bool in = i < dim;
                 kk[m] = in ? k[i] : 0.f;
-                s[m] *= in ? g[i] : 1.f;
+                s[m] *= in ? expf(g[i]) : 1.f;                      // `decay` holds logarithms
                 pred += s[m] * kk[m];
             }
             pred += __shfl_xor_sync(0xffffffffu, pred, 1);
@@ -251,6 +254,340 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) delta_scan_kernel(cons
         const int i = sub + SCAN_LANES * m;
         if (live && i < dim) state[(size_t)i * vdim + j] = s[m];
     }
+}
+
+// ----------------------------------------------------------------------------- the recurrence in chunks
+// Within a chunk of CH tokens that starts from the state S0, with L_t the sum of the decays' logarithms up to token t
+// of the chunk (per key channel), the recurrence unrolls to
+//     u_t = beta_t (v_t - S0^T (e^{L_t} k_t) - sum_{s<t} A[t,s] u_s),      A[t,s] = sum_c k_t[c] k_s[c] e^{L_t[c] - L_s[c]}
+//     o_t = S0^T (e^{L_t} q_t) + sum_{s<=t} B[t,s] u_s,                    B[t,s] = sum_c q_t[c] k_s[c] e^{L_t[c] - L_s[c]}
+//     S   = diag(e^{L_last}) S0 + sum_s (e^{L_last - L_s} k_s) u_s^T
+// Every exponent is a sum of logarithms of decays over a range of tokens, so it is <= 0: nothing is divided by a decay.
+// What does not depend on the state (the scaled keys and queries and the two triangles) is made for all chunks of all
+// heads at once by delta_chunk_prepare_kernel; delta_chunk_scan_kernel then walks the chunks of a sequence with the
+// state's columns in registers, and its work per chunk has no chain from token to token but the small triangular
+// solve.  All float; the result differs from the token-by-token kernel by rounding only.
+constexpr int CH = 16;
+
+struct ChunkParams {
+    const float* q; const float* k; const float* log_decay;      // [T, kv_heads, dim] x 2, [T, heads, dim]
+    float* kt; float* qt; float* kb; float* gc;                    // [T, heads, dim]: e^{L_t} k_t, e^{L_t} q_t, e^{L_last - L_t} k_t; e^{L_last} in a chunk's first row
+    float* ab;                                                     // [T, heads, 2 CH]: for token s, A[t, s] for every t of its chunk (0 unless s < t), then B[t, s] (0 unless s <= t)
+    const int* seq_start;
+    int heads, kv_heads, dim;
+};
+
+// grid (chunks of the longest sequence, heads, sequences), 128 threads.
+__global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int dim = p.dim, head = blockIdx.y, seq = blockIdx.z;
+    const int kvh = head / (p.heads / p.kv_heads);
+    const int row0 = p.seq_start[seq], count = p.seq_start[seq + 1] - row0;
+    const int first = blockIdx.x * CH;
+    if (first >= count) return;
+    const int n = min(CH, count - first);
+    float* qs = sm;                       // [CH][dim]
+    float* ks = qs + CH * dim;            // [CH][dim]
+    float* ls = ks + CH * dim;            // [CH][dim] running sums of the logarithms
+    for (int e = threadIdx.x; e < CH * dim; e += blockDim.x) {
+        const int tt = e / dim, c = e % dim;
+        const size_t t = (size_t)(row0 + first + tt);
+        const bool in = tt < n;
+        qs[e] = in ? p.q[(t * p.kv_heads + kvh) * dim + c] : 0.f;
+        ks[e] = in ? p.k[(t * p.kv_heads + kvh) * dim + c] : 0.f;
+        ls[e] = in ? p.log_decay[(t * p.heads + head) * dim + c] : 0.f;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        float run = 0.f;
+        for (int tt = 0; tt < CH; ++tt) { run += ls[tt * dim + c]; ls[tt * dim + c] = run; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
+        const int tt = e / dim, c = e % dim;
+        const size_t at = ((size_t)(row0 + first + tt) * p.heads + head) * dim + c;
+        const float grow = expf(ls[e]), rest = expf(ls[(n - 1) * dim + c] - ls[e]);
+        p.kt[at] = grow * ks[e];
+        p.qt[at] = grow * qs[e];
+        p.kb[at] = rest * ks[e];
+        if (tt == 0) p.gc[at] = expf(ls[(n - 1) * dim + c]);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int pair = warp; pair < CH * CH; pair += 4) {
+        const int s = pair / CH, t = pair % CH;
+        if (s >= n) break;
+        float a = 0.f, b = 0.f;
+        if (s <= t && t < n) {
+            for (int c = lane; c < dim; c += 32) {
+                const float w = ks[s * dim + c] * expf(ls[t * dim + c] - ls[s * dim + c]);
+                a += ks[t * dim + c] * w;
+                b += qs[t * dim + c] * w;
+            }
+            a = warp_sum(a);
+            b = warp_sum(b);
+        }
+        if (lane == 0) {
+            float* row = p.ab + ((size_t)(row0 + first + s) * p.heads + head) * 2 * CH;
+            row[t] = s < t ? a : 0.f;
+            row[CH + t] = b;
+        }
+    }
+}
+
+struct ChunkScanParams {
+    const float* kt; const float* qt; const float* kb; const float* gc; const float* ab;
+    const float* v; const float* beta;
+    float* state; float* out;
+    const int* seq_start; const int* slots;
+    int heads, dim, vdim;
+};
+
+// grid (column blocks, heads, sequences); threads as in delta_scan_kernel: a column of the state belongs to 8 neighbouring
+// lanes, lane s of them holding rows s, s + 8, ...
+template <int R>
+__global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) delta_chunk_scan_kernel(const ChunkScanParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int dim = p.dim, vdim = p.vdim;
+    const int per_token = 3 * dim + 2 * CH + SCAN_COLS + 1;       // kt, qt, kb rows, the A and B rows, the block's v columns, beta
+    const int per_chunk = CH * per_token + dim;                   // and the chunk's whole decay
+    float* buffers[2] = {sm, sm + per_chunk};
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int col = threadIdx.x / SCAN_LANES, sub = threadIdx.x % SCAN_LANES;
+    const int j = blockIdx.x * SCAN_COLS + col;
+    const bool live = j < vdim;
+    const int row0 = p.seq_start[seq], count = p.seq_start[seq + 1] - row0;
+    float* state = p.state + ((size_t)p.slots[seq] * p.heads + head) * dim * vdim;
+
+    float s[R];
+#pragma unroll
+    for (int m = 0; m < R; ++m) {
+        const int i = sub + SCAN_LANES * m;
+        s[m] = (live && i < dim) ? state[(size_t)i * vdim + j] : 0.f;
+    }
+    auto fetch = [&](int chunk, float* buf) {
+        const int first = chunk * CH, n = min(CH, count - first);
+        for (int e = threadIdx.x; e < n * per_token + dim; e += blockDim.x) {
+            const float* src;
+            float* dst;
+            if (e < n * per_token) {
+                const int tt = e / per_token, c = e % per_token;
+                const size_t at = (size_t)(row0 + first + tt) * p.heads + head;
+                if (c < dim) src = p.kt + at * dim + c;
+                else if (c < 2 * dim) src = p.qt + at * dim + (c - dim);
+                else if (c < 3 * dim) src = p.kb + at * dim + (c - 2 * dim);
+                else if (c < 3 * dim + 2 * CH) src = p.ab + at * 2 * CH + (c - 3 * dim);
+                else if (c < 3 * dim + 2 * CH + SCAN_COLS) {
+                    const int jj = blockIdx.x * SCAN_COLS + (c - 3 * dim - 2 * CH);
+                    src = p.v + at * vdim + (jj < vdim ? jj : vdim - 1);
+                } else src = p.beta + at;
+                dst = buf + e;
+            } else {
+                src = p.gc + ((size_t)(row0 + first) * p.heads + head) * dim + (e - n * per_token);
+                dst = buf + CH * per_token + (e - n * per_token);
+            }
+            cp_async4(dst, src);
+        }
+        cp_async_commit();
+    };
+    const int chunks = (count + CH - 1) / CH;
+    if (chunks > 0) fetch(0, buffers[0]);
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+        cp_async_wait_all();
+        __syncthreads();
+        if (chunk + 1 < chunks) fetch(chunk + 1, buffers[(chunk + 1) & 1]);
+        const float* buf = buffers[chunk & 1];
+        const int n = min(CH, count - chunk * CH);
+        // what the state holds for every token of the chunk: S0^T (e^L k_t) and S0^T (e^L q_t), summed over the 8 lanes of the column
+        float pred[CH], read[CH];
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+            float a = 0.f, b = 0.f;
+            if (tt < n) {
+                const float* kt = buf + tt * per_token;
+                const float* qt = kt + dim;
+#pragma unroll
+                for (int m = 0; m < R; ++m) {
+                    const int i = sub + SCAN_LANES * m;
+                    if (i < dim) { a += kt[i] * s[m]; b += qt[i] * s[m]; }
+                }
+            }
+            pred[tt] = a;
+            read[tt] = b;
+        }
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+            pred[tt] += __shfl_xor_sync(0xffffffffu, pred[tt], 1);
+            read[tt] += __shfl_xor_sync(0xffffffffu, read[tt], 1);
+            pred[tt] += __shfl_xor_sync(0xffffffffu, pred[tt], 2);
+            read[tt] += __shfl_xor_sync(0xffffffffu, read[tt], 2);
+            pred[tt] += __shfl_xor_sync(0xffffffffu, pred[tt], 4);
+            read[tt] += __shfl_xor_sync(0xffffffffu, read[tt], 4);
+        }
+        // the triangular solve, the same in each of the column's lanes; pred[t] turns into u_t
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+            if (tt < n) {
+                const float* row = buf + tt * per_token + 3 * dim;            // the token's columns of A and B, v columns, beta
+                const float u = row[2 * CH + SCAN_COLS] * (row[2 * CH + col] - pred[tt]);
+                pred[tt] = u;
+#pragma unroll
+                for (int later = tt + 1; later < CH; ++later)
+                    if (later < n) pred[later] += row[later] * u;
+#pragma unroll
+                for (int later = tt; later < CH; ++later)
+                    if (later < n) read[later] += row[CH + later] * u;
+            }
+        }
+        if (sub == 0 && live) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt)
+                if (tt < n) p.out[((size_t)(row0 + chunk * CH + tt) * p.heads + head) * vdim + j] = read[tt];
+        }
+        // the state behind the chunk
+        const float* gc = buf + CH * per_token;
+#pragma unroll
+        for (int m = 0; m < R; ++m) {
+            const int i = sub + SCAN_LANES * m;
+            if (i < dim) {
+                float acc = gc[i] * s[m];
+#pragma unroll
+                for (int tt = 0; tt < CH; ++tt)
+                    if (tt < n) acc += buf[tt * per_token + 2 * dim + i] * pred[tt];
+                s[m] = acc;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < R; ++m) {
+        const int i = sub + SCAN_LANES * m;
+        if (live && i < dim) state[(size_t)i * vdim + j] = s[m];
+    }
+}
+
+// The same walk for the usual sizes (dim a multiple of 64 up to 256, vdim a multiple of 16), written for few instructions:
+// a column of the state belongs to CH = 16 neighbouring lanes, lane l of them holding the rows 4 (l + 16 q) + e
+// (q < RQ, e < 4: 16-byte pieces that the 16 lanes read side by side) and owning the scalars of the chunk's token l.
+// The per-token sums over the state's rows are reduced so that token l's sum lands in lane l (15 exchanges instead of
+// 64), the triangular solve passes each u_t on by one shuffle, and chunk data arrives by 16-byte copies; a chunk's
+// missing tokens are zeros, which change nothing.  grid (vdim / 16, heads, sequences), 256 threads.
+constexpr int FAST_COLS = 16;
+
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int RQ>
+__global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(const ChunkScanParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int DIM = 64 * RQ;
+    constexpr int PER_TOKEN = 3 * DIM + 2 * CH + FAST_COLS + 4;   // kt, qt, kb rows, A and B columns, v columns, beta (padded to 16 bytes)
+    constexpr int PER_CHUNK = CH * PER_TOKEN + DIM;
+    float* buffers[2] = {sm, sm + PER_CHUNK};
+    const int vdim = p.vdim, head = blockIdx.y, seq = blockIdx.z;
+    const int lane = threadIdx.x & 31, l = threadIdx.x & 15, col = threadIdx.x >> 4;
+    const int j = blockIdx.x * FAST_COLS + col;
+    const int row0 = p.seq_start[seq], count = p.seq_start[seq + 1] - row0;
+    float* state = p.state + ((size_t)p.slots[seq] * p.heads + head) * DIM * vdim;
+
+    float s[RQ][4];
+#pragma unroll
+    for (int q = 0; q < RQ; ++q)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[q][e] = state[(size_t)(4 * (l + 16 * q) + e) * vdim + j];
+
+    auto fetch = [&](int chunk, float* buf) {
+        const int first = chunk * CH, n = min(CH, count - first);
+        constexpr int PIECES = PER_TOKEN / 4;                      // 16-byte pieces of a token's data
+        for (int e = threadIdx.x; e < CH * PIECES; e += blockDim.x) {
+            const int tt = e / PIECES, c = 4 * (e % PIECES);
+            float* dst = buf + tt * PER_TOKEN + c;
+            if (tt >= n) { *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f); continue; }
+            const size_t at = (size_t)(row0 + first + tt) * p.heads + head;
+            if (c < DIM) cp_async16(dst, p.kt + at * DIM + c);
+            else if (c < 2 * DIM) cp_async16(dst, p.qt + at * DIM + (c - DIM));
+            else if (c < 3 * DIM) cp_async16(dst, p.kb + at * DIM + (c - 2 * DIM));
+            else if (c < 3 * DIM + 2 * CH) cp_async16(dst, p.ab + at * 2 * CH + (c - 3 * DIM));
+            else if (c < 3 * DIM + 2 * CH + FAST_COLS) cp_async16(dst, p.v + at * vdim + blockIdx.x * FAST_COLS + (c - 3 * DIM - 2 * CH));
+            else *reinterpret_cast<float4*>(dst) = make_float4(p.beta[at], 0.f, 0.f, 0.f);
+        }
+        for (int e = threadIdx.x; e < DIM / 4; e += blockDim.x)
+            cp_async16(buf + CH * PER_TOKEN + 4 * e, p.gc + ((size_t)(row0 + first) * p.heads + head) * DIM + 4 * e);
+        cp_async_commit();
+    };
+    const int chunks = (count + CH - 1) / CH;
+    if (chunks > 0) fetch(0, buffers[0]);
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+        cp_async_wait_all();
+        __syncthreads();
+        if (chunk + 1 < chunks) fetch(chunk + 1, buffers[(chunk + 1) & 1]);
+        const float* buf = buffers[chunk & 1];
+        const int n = min(CH, count - chunk * CH);
+        // this lane's share of S0^T (e^L k_t) and S0^T (e^L q_t) for every token of the chunk
+        float pred[CH], read[CH];
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int q = 0; q < RQ; ++q) {
+                const float4 kt = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + 4 * (l + 16 * q));
+                const float4 qt = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + DIM + 4 * (l + 16 * q));
+                a += kt.x * s[q][0] + kt.y * s[q][1] + kt.z * s[q][2] + kt.w * s[q][3];
+                b += qt.x * s[q][0] + qt.y * s[q][1] + qt.z * s[q][2] + qt.w * s[q][3];
+            }
+            pred[tt] = a;
+            read[tt] = b;
+        }
+        // sums over the 16 lanes of the column, token l's landing in lane l: halve the tokens a lane carries four times
+#pragma unroll
+        for (int step = 8; step >= 1; step >>= 1) {
+            const bool upper = (l & step) != 0;
+#pragma unroll
+            for (int i = 0; i < step; ++i) {
+                const float give_p = upper ? pred[i] : pred[i + step], keep_p = upper ? pred[i + step] : pred[i];
+                const float give_r = upper ? read[i] : read[i + step], keep_r = upper ? read[i + step] : read[i];
+                pred[i] = keep_p + __shfl_xor_sync(0xffffffffu, give_p, step);
+                read[i] = keep_r + __shfl_xor_sync(0xffffffffu, give_r, step);
+            }
+        }
+        // lane l now holds token l's sums in pred[0] and read[0]
+        float mine_p = pred[0], mine_r = read[0];
+        const float beta = buf[l * PER_TOKEN + 3 * DIM + 2 * CH + FAST_COLS];
+        const float vj = buf[l * PER_TOKEN + 3 * DIM + 2 * CH + col];
+        float u[CH];
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+            const float candidate = beta * (vj - mine_p);                       // u of this lane's token, final once tt reaches it
+            u[tt] = __shfl_sync(0xffffffffu, candidate, (lane & 16) + tt);
+            const float* column = buf + tt * PER_TOKEN + 3 * DIM;              // what u_tt adds to the later tokens
+            mine_p += column[l] * u[tt];                                        // zero unless l > tt
+            mine_r += column[CH + l] * u[tt];                                   // zero unless l >= tt
+        }
+        if (l < n) p.out[((size_t)(row0 + chunk * CH + l) * p.heads + head) * vdim + j] = mine_r;
+        // the state behind the chunk
+        const float* gc = buf + CH * PER_TOKEN;
+#pragma unroll
+        for (int q = 0; q < RQ; ++q) {
+            const float4 g = *reinterpret_cast<const float4*>(gc + 4 * (l + 16 * q));
+            float acc[4] = {g.x * s[q][0], g.y * s[q][1], g.z * s[q][2], g.w * s[q][3]};
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) {
+                const float4 kb = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + 2 * DIM + 4 * (l + 16 * q));
+                acc[0] += kb.x * u[tt]; acc[1] += kb.y * u[tt]; acc[2] += kb.z * u[tt]; acc[3] += kb.w * u[tt];
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[q][e] = acc[e];
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < RQ; ++q)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) state[(size_t)(4 * (l + 16 * q) + e) * vdim + j] = s[q][e];
 }
 
 // out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * gate[t, h, :].  One warp per (token, head).
@@ -322,7 +659,7 @@ static int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
     const size_t smem = 2 * (size_t)SCAN_CHUNK * (3 * p.dim + SCAN_COLS + 1) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(delta_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaError_t err = cudaFuncSetAttribute(delta_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "delta_scan: cannot raise shared memory: %s", cudaGetErrorString(err));
         configured = true;
     }
@@ -345,6 +682,72 @@ extern "C" int qt_delta_scan(const float* q, const float* k, const float* v, con
     if (dim <= 128) return launch_scan<16>(p, n_seqs, s);
     if (dim <= 256) return launch_scan<32>(p, n_seqs, s);
     return launch_scan<64>(p, n_seqs, s);
+}
+
+template <int R>
+static int launch_chunk_scan(const ChunkScanParams& p, int n_seqs, cudaStream_t s) {
+    const size_t smem = 2 * ((size_t)CH * (3 * p.dim + 2 * CH + SCAN_COLS + 1) + p.dim) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(delta_chunk_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "delta_chunk_scan: cannot raise shared memory: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    QT_REQUIRE(smem <= 220 * 1024, "delta_chunk_scan: %d key channels per head need more shared memory than a block has", p.dim);
+    launch_kernel(delta_chunk_scan_kernel<R>, dim3((p.vdim + SCAN_COLS - 1) / SCAN_COLS, p.heads, n_seqs), dim3(SCAN_COLS * SCAN_LANES), smem, s, p);
+    QT_CHECK_LAUNCH("delta_chunk_scan");
+    return QT_OK;
+}
+
+template <int RQ>
+static int launch_chunk_scan_fast(const ChunkScanParams& p, int n_seqs, cudaStream_t s) {
+    const size_t smem = 2 * ((size_t)CH * (3 * 64 * RQ + 2 * CH + FAST_COLS + 4) + 64 * RQ) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(delta_chunk_scan_fast_kernel<RQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "delta_chunk_scan: cannot raise shared memory: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    launch_kernel(delta_chunk_scan_fast_kernel<RQ>, dim3(p.vdim / FAST_COLS, p.heads, n_seqs), dim3(FAST_COLS * CH), smem, s, p);
+    QT_CHECK_LAUNCH("delta_chunk_scan");
+    return QT_OK;
+}
+
+// The recurrence in chunks (steps of many tokens per sequence).  Scratch of the caller: kt, qt, kb, gc [T, heads, dim] and
+// ab [T, heads, 32], float.  `max_tokens` is the most tokens any sequence of the step has.
+extern "C" int qt_delta_scan_chunked(const float* q, const float* k, const float* v, const float* beta, const float* log_decay,
+                                     float* state, float* out, float* kt, float* qt, float* kb, float* gc, float* ab,
+                                     const int* seq_start, const int* slots, int n_seqs, int max_tokens, int heads, int kv_heads,
+                                     int dim, int vdim, void* stream) {
+    QT_REQUIRE(n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && vdim > 0 && max_tokens >= 0, "delta_scan_chunked: bad sizes");
+    QT_REQUIRE(dim > 0 && dim <= 256, "delta_scan_chunked: %d key channels per head (1..256)", dim);
+    QT_REQUIRE(n_seqs <= 65535 && heads <= 65535, "delta_scan_chunked: too many sequences or heads for one launch");
+    if (n_seqs == 0 || max_tokens == 0) return QT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    ChunkParams cp{q, k, log_decay, kt, qt, kb, gc, ab, seq_start, heads, kv_heads, dim};
+    const size_t smem = 3 * (size_t)CH * dim * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(delta_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "delta_chunk_prepare: cannot raise shared memory: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    launch_kernel(delta_chunk_prepare_kernel, dim3((max_tokens + CH - 1) / CH, heads, n_seqs), dim3(128), smem, s, cp);
+    QT_CHECK_LAUNCH("delta_chunk_prepare");
+    ChunkScanParams sp{kt, qt, kb, gc, ab, v, beta, state, out, seq_start, slots, heads, dim, vdim};
+    static const bool plain_only = [] { const char* env = getenv("QT_B200_DELTA_FAST"); return env && env[0] == '0'; }();
+    const bool aligned = ((uintptr_t)kt % 16 == 0) && ((uintptr_t)qt % 16 == 0) && ((uintptr_t)kb % 16 == 0) && ((uintptr_t)gc % 16 == 0) &&
+                         ((uintptr_t)ab % 16 == 0) && ((uintptr_t)v % 16 == 0);
+    if (!plain_only && aligned && dim % 64 == 0 && dim <= 256 && vdim % FAST_COLS == 0) {
+        if (dim == 64) return launch_chunk_scan_fast<1>(sp, n_seqs, s);
+        if (dim == 128) return launch_chunk_scan_fast<2>(sp, n_seqs, s);
+        if (dim == 192) return launch_chunk_scan_fast<3>(sp, n_seqs, s);
+        return launch_chunk_scan_fast<4>(sp, n_seqs, s);
+    }
+    if (dim <= 32) return launch_chunk_scan<4>(sp, n_seqs, s);
+    if (dim <= 64) return launch_chunk_scan<8>(sp, n_seqs, s);
+    if (dim <= 128) return launch_chunk_scan<16>(sp, n_seqs, s);
+    return launch_chunk_scan<32>(sp, n_seqs, s);
 }
 
 extern "C" int qt_gated_head_norm(const float* o, const float* gate, const float* w, float eps, void* out, int out_dtype,

@@ -43,6 +43,8 @@ _SIGNATURES = {
         "qt_lowrank": [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
         "qt_delta_scan": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
         "qt_gated_head_norm": [_c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_delta_scan_chunked": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "attention": {
         "qt_attention_prefill": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
@@ -407,7 +409,7 @@ def lowrank(proj: GemmOut, offset: int, weight: torch.Tensor, out: torch.Tensor,
             rate_log: torch.Tensor | None = None, per_rate: int = 0) -> None:
     """out [T, N] (float) = f(weight^T x + bias) for x = columns ``offset`` .. ``offset + rank`` of ``proj`` and
     ``weight`` [rank, N] (float, the second matrix of a projection through a few columns, transposed).  With
-    ``rate_log`` [N / per_rate] f is a decay, exp(-exp(rate_log[n / per_rate]) * softplus(.)); else the sigmoid."""
+    ``rate_log`` [N / per_rate] f is the logarithm of a decay, -exp(rate_log[n / per_rate]) * softplus(.); else the sigmoid."""
     rank, n_out = weight.shape
     _need(proj.tensor, "proj", torch.float32)
     _need(weight, "weight", torch.float32)
@@ -423,8 +425,9 @@ def lowrank(proj: GemmOut, offset: int, weight: torch.Tensor, out: torch.Tensor,
 def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
                out: torch.Tensor, ctx) -> None:
     """The gated delta rule over the tokens of every sequence of the step, from and into ``state``
-    [slots + 1, heads, dim, vdim] (float): S <- diag(decay_t) S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T;
-    out_t = S^T q_t.  q, k [T, kv_heads, dim]; v, out [T, heads, vdim]; beta [T, heads]; decay [T, heads, dim]."""
+    [slots + 1, heads, dim, vdim] (float): S <- diag(exp(decay_t)) S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T;
+    out_t = S^T q_t.  q, k [T, kv_heads, dim]; v, out [T, heads, vdim]; beta [T, heads]; decay [T, heads, dim], the decays'
+    logarithms.  Token by token: the form for steps of few tokens per sequence."""
     tokens, heads, vdim = v.shape
     kv_heads, dim = q.shape[1], q.shape[2]
     for name, tensor, shape in (("q", q, (tokens, kv_heads, dim)), ("k", k, (tokens, kv_heads, dim)), ("v", v, (tokens, heads, vdim)),
@@ -435,6 +438,34 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
         raise KernelError(f"delta_scan: state {tuple(state.shape)} is not [slots, {heads}, {dim}, {vdim}]")
     _call("delta_rule", "qt_delta_scan", _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), _ptr(out), _ptr(ctx.seq_start),
           _ptr(ctx.slots), ctx.n_seqs, heads, kv_heads, dim, vdim, _stream())
+
+
+DELTA_CHUNK = 16               # tokens per chunk of the chunked recurrence
+DELTA_CHUNKED_MAX_DIM = 256    # key channels per head it takes
+
+
+def delta_scan_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                       out: torch.Tensor, scratch: torch.Tensor, ctx) -> None:
+    """The same recurrence as ``delta_scan`` in chunks of 16 tokens: what does not depend on the state (keys and queries
+    scaled by the running decays, the chunk's two triangular matrices) is made for all chunks at once, and the walk over
+    a sequence's chunks has no chain from token to token.  Float throughout; results differ from the token-by-token
+    form by rounding.  ``scratch``: float, at least T * heads * (4 * dim + 32) elements."""
+    tokens, heads, vdim = v.shape
+    kv_heads, dim = q.shape[1], q.shape[2]
+    for name, tensor, shape in (("q", q, (tokens, kv_heads, dim)), ("k", k, (tokens, kv_heads, dim)), ("v", v, (tokens, heads, vdim)),
+                                ("beta", beta, (tokens, heads)), ("decay", decay, (tokens, heads, dim)), ("out", out, (tokens, heads, vdim))):
+        _need(tensor, name, torch.float32, shape)
+    _need(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError(f"delta_scan_chunked: state {tuple(state.shape)} is not [slots, {heads}, {dim}, {vdim}]")
+    _need(scratch, "scratch", torch.float32)
+    rows = tokens * heads * dim
+    if scratch.numel() < 4 * rows + tokens * heads * 2 * DELTA_CHUNK:
+        raise KernelError("delta_scan_chunked: the scratch buffer is too small")
+    parts = [scratch[i * rows:(i + 1) * rows] for i in range(4)] + [scratch[4 * rows:]]
+    _call("delta_rule", "qt_delta_scan_chunked", _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), _ptr(out),
+          *[_ptr(part) for part in parts], _ptr(ctx.seq_start), _ptr(ctx.slots), ctx.n_seqs, int(ctx.max_q_len), heads, kv_heads, dim, vdim,
+          _stream(), launches=2)
 
 
 def gated_head_norm(o: torch.Tensor, gate: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:

@@ -11,7 +11,8 @@ so the read-out sees the token's own write.  Around it:
   the sequence's start) and SiLU; q and k are then made unit vectors per head, x / sqrt(sum x^2 + 1e-6), q also
   times dim^-1/2;
 * beta = sigmoid(W_b h), one per head;
-* g = exp(-exp(A_log_h) softplus(W_a2 (W_a1 h) + dt_bias)), [heads, dim]: a projection through few columns;
+* g = exp(-exp(A_log_h) softplus(W_a2 (W_a1 h) + dt_bias)), [heads, dim]: a projection through few columns (the
+  kernels pass its logarithm on);
 * every head's o is divided by its root mean square over vdim (``eps`` inside the root), times a weight [vdim] shared
   by the heads, times sigmoid(W_g2 (W_g1 h)) ([heads, vdim]); then W_o.
 
@@ -35,6 +36,7 @@ from .base import Runtime, StateRequest, register_mixer, to_device
 from .linear import Linear
 
 _UNIT_EPS = 1e-6      # inside the root of the unit norms of q and k
+_FEW_TOKENS = 4       # steps in which no sequence brings more tokens run the recurrence token by token
 
 
 @register_mixer("gated_delta_rule")
@@ -76,6 +78,7 @@ class GatedDeltaRule:
                             ("delta.read", self.heads * self.vdim)):
             ws.declare(name, tokens * width, torch.float32)
         ws.declare("delta.normed", tokens * self.heads * self.vdim, runtime.dtype)
+        ws.declare("delta.chunks", tokens * self.heads * (4 * self.dim + 2 * kernels.DELTA_CHUNK), torch.float32)
         self.conv = self.decay_out = self.decay_bias = self.decay_rate = self.gate_out = self.norm = None
 
     # ------------------------------------------------------------------ weights
@@ -159,7 +162,11 @@ class GatedDeltaRule:
         kernels.delta_prepare(proj, self.conv, kept_rows, ctx, q, k, v, beta, self.heads, self.kv_heads, self.dim, self.vdim, _UNIT_EPS)
         kernels.lowrank(proj, self.at_decay, self.decay_out, decay.view(tokens, self.heads * self.dim), self.decay_bias, self.decay_rate, self.dim)
         kernels.lowrank(proj, self.at_gate, self.gate_out, gate.view(tokens, self.heads * self.vdim))
-        kernels.delta_scan(q, k, v, beta, decay, states.state, read, ctx)
+        if ctx.max_q_len > _FEW_TOKENS and self.dim <= kernels.DELTA_CHUNKED_MAX_DIM:
+            kernels.delta_scan_chunked(q, k, v, beta, decay, states.state, read,
+                                       ws.view("delta.chunks", tokens * self.heads * (4 * self.dim + 2 * kernels.DELTA_CHUNK)), ctx)
+        else:
+            kernels.delta_scan(q, k, v, beta, decay, states.state, read, ctx)
         normed = ws.view("delta.normed", tokens, self.heads, self.vdim)
         kernels.gated_head_norm(read, gate, self.norm, self.eps, normed)
         return self.o(normed.view(tokens, self.heads * self.vdim))

@@ -266,13 +266,25 @@ class _Step:
             starts.append(starts[-1] + n)
         as_int = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)
         self.n_seqs = len(lengths)
+        self.max_q_len = max(lengths)
         self.seq_start, self.seq_past, self.slots = as_int(starts), as_int(past), as_int(slots)
         self.token_seq = as_int([s for s, n in enumerate(lengths) for _ in range(n)])
         self.token_pos = as_int([past[s] + i for s, n in enumerate(lengths) for i in range(n)])
 
 
-@pytest.mark.parametrize("heads, kv_heads, dim, vdim, taps", [(2, 1, 16, 32, 4), (3, 3, 12, 20, 1), (4, 2, 36, 8, 7), (1, 1, 72, 136, 2), (2, 2, 130, 40, 3)])
-def test_delta_rule_kernels_in_portions_of_two_sequences(heads, kv_heads, dim, vdim, taps):
+def scan(chunked, q, k, v, beta, decay, states, read, step):
+    """The recurrence token by token, or in chunks of 16 tokens."""
+    if not chunked:
+        return kernels.delta_scan(q, k, v, beta, decay, states, read, step)
+    tokens, heads, _ = v.shape
+    scratch = torch.empty(tokens * heads * (4 * q.shape[2] + 2 * kernels.DELTA_CHUNK), device=DEV)
+    kernels.delta_scan_chunked(q, k, v, beta, decay, states, read, scratch, step)
+
+
+@pytest.mark.parametrize("chunked", [False, True])
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, taps", [(2, 1, 16, 32, 4), (3, 3, 12, 20, 1), (4, 2, 36, 8, 7), (1, 1, 72, 136, 2), (2, 2, 130, 40, 3),
+                                                             (2, 1, 64, 32, 4), (1, 1, 128, 48, 2), (2, 2, 256, 16, 3), (1, 1, 192, 16, 1)])
+def test_delta_rule_kernels_in_portions_of_two_sequences(heads, kv_heads, dim, vdim, taps, chunked):
     """Projection output -> convolution, SiLU, unit norms, decays, recurrence, gated head norm, for two sequences whose
     tokens arrive in unequal portions (one of a single token), the states and the convolutions' last inputs carried
     in slots that are not in order; against the plain mixer on the whole sequences."""
@@ -315,7 +327,7 @@ def test_delta_rule_kernels_in_portions_of_two_sequences(heads, kv_heads, dim, v
                         tensors["m.A_log"].to(DEV), dim)
         kernels.lowrank(proj, channels + heads + ra, tensors["m.g2"].t().contiguous().to(DEV), gate.view(tokens, -1))
         read = torch.empty(tokens, heads, vdim, device=DEV)
-        kernels.delta_scan(q, k, v, beta, decay, states, read, step)
+        scan(chunked, q, k, v, beta, decay, states, read, step)
         out = torch.empty(tokens, heads, vdim, device=DEV)
         kernels.gated_head_norm(read, gate, tensors["m.norm"].to(DEV), eps, out)
         at = 0
@@ -330,7 +342,8 @@ def test_delta_rule_kernels_in_portions_of_two_sequences(heads, kv_heads, dim, v
         torch.testing.assert_close(torch.cat(got[s]).reshape(lengths[s], -1), want.float(), atol=2e-4, rtol=2e-4)
 
 
-def test_delta_rule_state_keeps_a_far_write():
+@pytest.mark.parametrize("chunked", [False, True])
+def test_delta_rule_state_keeps_a_far_write(chunked):
     """One strong write at the first token, decays of nearly one, 600 tokens of small writes, and a query along the
     first key: what is read at the end is mostly the first token's value."""
     heads, dim, vdim, tokens = 1, 16, 8, 600
@@ -344,7 +357,7 @@ def test_delta_rule_state_keeps_a_far_write():
     decay = torch.full((tokens, heads, dim), 0.9999)
     state = torch.zeros(2, heads, dim, vdim, device=DEV)
     read = torch.empty(tokens, heads, vdim, device=DEV)
-    kernels.delta_scan(q.to(DEV), k.to(DEV), v.to(DEV), beta.to(DEV), decay.to(DEV), state, read, _Step([tokens], [0], [0]))
+    scan(chunked, q.to(DEV), k.to(DEV), v.to(DEV), beta.to(DEV), decay.log().to(DEV), state, read, _Step([tokens], [0], [0]))
     s = torch.zeros(dim, vdim, dtype=torch.float64)
     for t in range(tokens):
         s = s * decay[t, 0].double()[:, None]
@@ -353,6 +366,31 @@ def test_delta_rule_state_keeps_a_far_write():
     torch.testing.assert_close(read[-1, 0].cpu(), (s.T @ q[-1, 0].double()).float(), atol=1e-4, rtol=1e-4)
     assert float(read[-1, 0, -1]) > 0.5 * vdim * 0.5          # the first value is still most of what is read
     torch.testing.assert_close(state[0, 0].cpu(), s.float(), atol=1e-4, rtol=1e-4)
+
+
+def test_chunked_recurrence_with_decays_that_underflow():
+    """Decays down to e^-30 a token: over a chunk their product is far below what a float holds, and the chunked form,
+    which only ever multiplies by products of decays over ranges, still agrees with the token-by-token form."""
+    torch.manual_seed(3)
+    run_chunked_with_strong_decays(2, 24, 40, 70)
+    run_chunked_with_strong_decays(2, 128, 32, 70)          # the sizes of the 16-lanes-per-column kernel
+
+
+def run_chunked_with_strong_decays(heads, dim, vdim, tokens):
+    q = torch.nn.functional.normalize(torch.randn(tokens, 1, dim), dim=-1).to(DEV)
+    k = torch.nn.functional.normalize(torch.randn(tokens, 1, dim), dim=-1).to(DEV)
+    v = torch.randn(tokens, heads, vdim, device=DEV)
+    beta = torch.rand(tokens, heads, device=DEV)
+    decay = -(torch.rand(tokens, heads, dim, device=DEV) ** 4) * 30.0
+    results = []
+    for chunked in (False, True):
+        state = torch.zeros(1, heads, dim, vdim, device=DEV)
+        read = torch.empty(tokens, heads, vdim, device=DEV)
+        scan(chunked, q, k, v, beta, decay, state, read, _Step([tokens], [0], [0]))
+        results.append((read, state))
+    assert bool(torch.isfinite(results[1][0]).all())
+    torch.testing.assert_close(results[1][0], results[0][0], atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(results[1][1], results[0][1], atol=1e-5, rtol=1e-4)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
