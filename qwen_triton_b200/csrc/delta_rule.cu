@@ -66,14 +66,25 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const PrepareParams 
                : is_k ? p.k + ((size_t)t * p.kv_heads + item - p.kv_heads) * p.dim
                       : p.v + ((size_t)t * p.heads + item - 2 * p.kv_heads) * p.vdim;
     float sq = 0.f;
+    const float* __restrict__ proj = p.proj;
+    const float* __restrict__ taps = p.taps;
     for (int i = lane; i < width; i += 32) {
         const int c = c0 + i;
         float acc = 0.f;
-        for (int back = 0; back < p.n_taps; ++back) {
-            float x;
-            if (back <= local) x = load_sum(p.proj, row - (size_t)back * p.proj_cols + c, p.n_splits, p.split_stride);
-            else x = kept[(size_t)(p.n_taps - 1 - (back - local)) * channels + c];
-            acc += p.taps[(size_t)c * p.n_taps + p.n_taps - 1 - back] * x;
+        for (int back0 = 0; back0 < p.n_taps; back0 += 4) {           // four taps at a time: their loads go out together
+            float x[4], w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int back = back0 + j;
+                x[j] = w[j] = 0.f;
+                if (back < p.n_taps) {
+                    w[j] = taps[(size_t)c * p.n_taps + p.n_taps - 1 - back];
+                    if (back <= local) x[j] = load_sum(proj, row - (size_t)back * p.proj_cols + c, p.n_splits, p.split_stride);
+                    else x[j] = kept[(size_t)(p.n_taps - 1 - (back - local)) * channels + c];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc += w[j] * x[j];
         }
         const float y = acc / (1.f + expf(-acc));
         out[i] = y;
@@ -132,10 +143,17 @@ __global__ void __launch_bounds__(256) lowrank_kernel(const float* __restrict__ 
     float acc[LR_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < LR_TOKENS; ++tt) acc[tt] = 0.f;
-    for (int r = 0; r < rank; ++r) {
-        const float wv = w[(size_t)r * n_out + n];
+    for (int r0 = 0; r0 < rank; r0 += 8) {                            // eight weights at a time: their loads go out together
+        float wv[8];
 #pragma unroll
-        for (int tt = 0; tt < LR_TOKENS; ++tt) acc[tt] += wv * xs[tt * rank + r];
+        for (int j = 0; j < 8; ++j) wv[j] = r0 + j < rank ? w[(size_t)(r0 + j) * n_out + n] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (r0 + j < rank) {
+#pragma unroll
+                for (int tt = 0; tt < LR_TOKENS; ++tt) acc[tt] += wv[j] * xs[tt * rank + r0 + j];
+            }
+        }
     }
     const float b = bias ? bias[n] : 0.f;
     const float rate = MODE == LR_DECAY ? expf(rate_log[n / per_rate]) : 0.f;
@@ -268,11 +286,13 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) delta_scan_kernel(cons
 // state's columns in registers, and its work per chunk has no chain from token to token but the small triangular
 // solve.  All float; the result differs from the token-by-token kernel by rounding only.
 constexpr int CH = 16;
+constexpr int AB = 2 * CH + 4;      // floats of a token's row of `ab`: its columns of the two triangles, beta, padding to 16 bytes
 
 struct ChunkParams {
     const float* q; const float* k; const float* log_decay;      // [T, kv_heads, dim] x 2, [T, heads, dim]
     float* kt; float* qt; float* kb; float* gc;                    // [T, heads, dim]: e^{L_t} k_t, e^{L_t} q_t, e^{L_last - L_t} k_t; e^{L_last} in a chunk's first row
-    float* ab;                                                     // [T, heads, 2 CH]: for token s, A[t, s] for every t of its chunk (0 unless s < t), then B[t, s] (0 unless s <= t)
+    const float* beta;                                             // [T, heads]
+    float* ab;                                                     // [T, heads, AB]: beta_s at [2 CH], and for token s, A[t, s] for every t of its chunk (0 unless s < t), then B[t, s] (0 unless s <= t)
     const int* seq_start;
     int heads, kv_heads, dim;
 };
@@ -329,9 +349,10 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkPar
             b = warp_sum(b);
         }
         if (lane == 0) {
-            float* row = p.ab + ((size_t)(row0 + first + s) * p.heads + head) * 2 * CH;
+            float* row = p.ab + ((size_t)(row0 + first + s) * p.heads + head) * AB;
             row[t] = s < t ? a : 0.f;
             row[CH + t] = b;
+            if (t == 0) row[2 * CH] = p.beta[(size_t)(row0 + first + s) * p.heads + head];
         }
     }
 }
@@ -379,7 +400,7 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) delta_chunk_scan_kerne
                 if (c < dim) src = p.kt + at * dim + c;
                 else if (c < 2 * dim) src = p.qt + at * dim + (c - dim);
                 else if (c < 3 * dim) src = p.kb + at * dim + (c - 2 * dim);
-                else if (c < 3 * dim + 2 * CH) src = p.ab + at * 2 * CH + (c - 3 * dim);
+                else if (c < 3 * dim + 2 * CH) src = p.ab + at * AB + (c - 3 * dim);
                 else if (c < 3 * dim + 2 * CH + SCAN_COLS) {
                     const int jj = blockIdx.x * SCAN_COLS + (c - 3 * dim - 2 * CH);
                     src = p.v + at * vdim + (jj < vdim ? jj : vdim - 1);
@@ -486,7 +507,7 @@ __global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(c
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
     constexpr int DIM = 64 * RQ;
-    constexpr int PER_TOKEN = 3 * DIM + 2 * CH + FAST_COLS + 4;   // kt, qt, kb rows, A and B columns, v columns, beta (padded to 16 bytes)
+    constexpr int PER_TOKEN = 3 * DIM + AB + FAST_COLS;           // kt, qt, kb rows, the token's row of `ab` (with beta), v columns
     constexpr int PER_CHUNK = CH * PER_TOKEN + DIM;
     float* buffers[2] = {sm, sm + PER_CHUNK};
     const int vdim = p.vdim, head = blockIdx.y, seq = blockIdx.z;
@@ -512,9 +533,8 @@ __global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(c
             if (c < DIM) cp_async16(dst, p.kt + at * DIM + c);
             else if (c < 2 * DIM) cp_async16(dst, p.qt + at * DIM + (c - DIM));
             else if (c < 3 * DIM) cp_async16(dst, p.kb + at * DIM + (c - 2 * DIM));
-            else if (c < 3 * DIM + 2 * CH) cp_async16(dst, p.ab + at * 2 * CH + (c - 3 * DIM));
-            else if (c < 3 * DIM + 2 * CH + FAST_COLS) cp_async16(dst, p.v + at * vdim + blockIdx.x * FAST_COLS + (c - 3 * DIM - 2 * CH));
-            else *reinterpret_cast<float4*>(dst) = make_float4(p.beta[at], 0.f, 0.f, 0.f);
+            else if (c < 3 * DIM + AB) cp_async16(dst, p.ab + at * AB + (c - 3 * DIM));
+            else cp_async16(dst, p.v + at * vdim + blockIdx.x * FAST_COLS + (c - 3 * DIM - AB));
         }
         for (int e = threadIdx.x; e < DIM / 4; e += blockDim.x)
             cp_async16(buf + CH * PER_TOKEN + 4 * e, p.gc + ((size_t)(row0 + first) * p.heads + head) * DIM + 4 * e);
@@ -557,8 +577,8 @@ __global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(c
         }
         // lane l now holds token l's sums in pred[0] and read[0]
         float mine_p = pred[0], mine_r = read[0];
-        const float beta = buf[l * PER_TOKEN + 3 * DIM + 2 * CH + FAST_COLS];
-        const float vj = buf[l * PER_TOKEN + 3 * DIM + 2 * CH + col];
+        const float beta = buf[l * PER_TOKEN + 3 * DIM + 2 * CH];
+        const float vj = buf[l * PER_TOKEN + 3 * DIM + AB + col];
         float u[CH];
 #pragma unroll
         for (int tt = 0; tt < CH; ++tt) {
@@ -642,13 +662,15 @@ extern "C" int qt_lowrank(const float* proj, int n_splits, long long split_strid
     QT_REQUIRE((size_t)LR_TOKENS * rank * sizeof(float) <= 48 * 1024, "lowrank: %d columns are too many for a tile in shared memory", rank);
     if (n_tokens == 0) return QT_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid((n_out + 255) / 256, (n_tokens + LR_TOKENS - 1) / LR_TOKENS);
+    // few tokens: blocks of 64 outputs, so that the one tile of tokens still gives many SMs a block
+    const int threads = n_tokens <= LR_TOKENS ? 64 : 256;
+    const dim3 grid((n_out + threads - 1) / threads, (n_tokens + LR_TOKENS - 1) / LR_TOKENS);
     const size_t smem = (size_t)LR_TOKENS * rank * sizeof(float);
     if (mode == LR_DECAY)
-        launch_kernel(lowrank_kernel<LR_DECAY>, grid, dim3(256), smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset, rank, w, bias,
+        launch_kernel(lowrank_kernel<LR_DECAY>, grid, dim3(threads), smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset, rank, w, bias,
                       rate_log, per_rate, out, n_tokens, n_out);
     else
-        launch_kernel(lowrank_kernel<LR_SIGMOID>, grid, dim3(256), smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset, rank, w, bias,
+        launch_kernel(lowrank_kernel<LR_SIGMOID>, grid, dim3(threads), smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset, rank, w, bias,
                       rate_log, per_rate, out, n_tokens, n_out);
     QT_CHECK_LAUNCH("lowrank");
     return QT_OK;
@@ -701,7 +723,7 @@ static int launch_chunk_scan(const ChunkScanParams& p, int n_seqs, cudaStream_t 
 
 template <int RQ>
 static int launch_chunk_scan_fast(const ChunkScanParams& p, int n_seqs, cudaStream_t s) {
-    const size_t smem = 2 * ((size_t)CH * (3 * 64 * RQ + 2 * CH + FAST_COLS + 4) + 64 * RQ) * sizeof(float);
+    const size_t smem = 2 * ((size_t)CH * (3 * 64 * RQ + AB + FAST_COLS) + 64 * RQ) * sizeof(float);
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(delta_chunk_scan_fast_kernel<RQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
@@ -714,7 +736,7 @@ static int launch_chunk_scan_fast(const ChunkScanParams& p, int n_seqs, cudaStre
 }
 
 // The recurrence in chunks (steps of many tokens per sequence).  Scratch of the caller: kt, qt, kb, gc [T, heads, dim] and
-// ab [T, heads, 32], float.  `max_tokens` is the most tokens any sequence of the step has.
+// ab [T, heads, 36], float.  `max_tokens` is the most tokens any sequence of the step has.
 extern "C" int qt_delta_scan_chunked(const float* q, const float* k, const float* v, const float* beta, const float* log_decay,
                                      float* state, float* out, float* kt, float* qt, float* kb, float* gc, float* ab,
                                      const int* seq_start, const int* slots, int n_seqs, int max_tokens, int heads, int kv_heads,
@@ -724,7 +746,7 @@ extern "C" int qt_delta_scan_chunked(const float* q, const float* k, const float
     QT_REQUIRE(n_seqs <= 65535 && heads <= 65535, "delta_scan_chunked: too many sequences or heads for one launch");
     if (n_seqs == 0 || max_tokens == 0) return QT_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    ChunkParams cp{q, k, log_decay, kt, qt, kb, gc, ab, seq_start, heads, kv_heads, dim};
+    ChunkParams cp{q, k, log_decay, kt, qt, kb, gc, beta, ab, seq_start, heads, kv_heads, dim};
     const size_t smem = 3 * (size_t)CH * dim * sizeof(float);
     static bool configured = false;
     if (!configured) {

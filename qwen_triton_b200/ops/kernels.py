@@ -449,7 +449,7 @@ def delta_scan_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: 
     """The same recurrence as ``delta_scan`` in chunks of 16 tokens: what does not depend on the state (keys and queries
     scaled by the running decays, the chunk's two triangular matrices) is made for all chunks at once, and the walk over
     a sequence's chunks has no chain from token to token.  Float throughout; results differ from the token-by-token
-    form by rounding.  ``scratch``: float, at least T * heads * (4 * dim + 32) elements."""
+    form by rounding.  ``scratch``: float, at least T * heads * (4 * dim + 36) elements."""
     tokens, heads, vdim = v.shape
     kv_heads, dim = q.shape[1], q.shape[2]
     for name, tensor, shape in (("q", q, (tokens, kv_heads, dim)), ("k", k, (tokens, kv_heads, dim)), ("v", v, (tokens, heads, vdim)),
@@ -460,7 +460,7 @@ def delta_scan_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: 
         raise KernelError(f"delta_scan_chunked: state {tuple(state.shape)} is not [slots, {heads}, {dim}, {vdim}]")
     _need(scratch, "scratch", torch.float32)
     rows = tokens * heads * dim
-    if scratch.numel() < 4 * rows + tokens * heads * 2 * DELTA_CHUNK:
+    if scratch.numel() < 4 * rows + tokens * heads * (2 * DELTA_CHUNK + 4):
         raise KernelError("delta_scan_chunked: the scratch buffer is too small")
     parts = [scratch[i * rows:(i + 1) * rows] for i in range(4)] + [scratch[4 * rows:]]
     _call("delta_rule", "qt_delta_scan_chunked", _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), _ptr(out),

@@ -78,7 +78,7 @@ class GatedDeltaRule:
                             ("delta.read", self.heads * self.vdim)):
             ws.declare(name, tokens * width, torch.float32)
         ws.declare("delta.normed", tokens * self.heads * self.vdim, runtime.dtype)
-        ws.declare("delta.chunks", tokens * self.heads * (4 * self.dim + 2 * kernels.DELTA_CHUNK), torch.float32)
+        ws.declare("delta.chunks", tokens * self.heads * (4 * self.dim + 2 * kernels.DELTA_CHUNK + 4), torch.float32)
         self.conv = self.decay_out = self.decay_bias = self.decay_rate = self.gate_out = self.norm = None
 
     # ------------------------------------------------------------------ weights
@@ -164,7 +164,7 @@ class GatedDeltaRule:
         kernels.lowrank(proj, self.at_gate, self.gate_out, gate.view(tokens, self.heads * self.vdim))
         if ctx.max_q_len > _FEW_TOKENS and self.dim <= kernels.DELTA_CHUNKED_MAX_DIM:
             kernels.delta_scan_chunked(q, k, v, beta, decay, states.state, read,
-                                       ws.view("delta.chunks", tokens * self.heads * (4 * self.dim + 2 * kernels.DELTA_CHUNK)), ctx)
+                                       ws.view("delta.chunks", tokens * self.heads * (4 * self.dim + 2 * kernels.DELTA_CHUNK + 4)), ctx)
         else:
             kernels.delta_scan(q, k, v, beta, decay, states.state, read, ctx)
         normed = ws.view("delta.normed", tokens, self.heads, self.vdim)

@@ -277,7 +277,7 @@ def scan(chunked, q, k, v, beta, decay, states, read, step):
     if not chunked:
         return kernels.delta_scan(q, k, v, beta, decay, states, read, step)
     tokens, heads, _ = v.shape
-    scratch = torch.empty(tokens * heads * (4 * q.shape[2] + 2 * kernels.DELTA_CHUNK), device=DEV)
+    scratch = torch.empty(tokens * heads * (4 * q.shape[2] + 2 * kernels.DELTA_CHUNK + 4), device=DEV)
     kernels.delta_scan_chunked(q, k, v, beta, decay, states, read, scratch, step)
 
 
