@@ -2,7 +2,7 @@
 //
 // Per head, with a state S [dim, vdim] of float that is carried from token to token of a sequence:
 //     S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
-// (the read-out sees the token's own write).  q and k come from kv heads (head h reads kv head h / (heads / kv_heads)),
+// (o_t is read after token t has been written).  q and k come from kv heads (head h reads kv head h / (heads / kv_heads)),
 // are unit vectors per head (q also times dim^-1/2), and q, k, v have passed a short causal convolution per channel and
 // SiLU.  Everything here is float whatever the model's element type: the projections before it hand over float sums.
 //

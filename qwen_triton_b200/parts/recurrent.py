@@ -4,7 +4,7 @@ Per head a float state S [dim, vdim] is carried from token to token of a sequenc
 
     S <- diag(g_t) S;   u_t = beta_t (v_t - S^T k_t);   S <- S + k_t u_t^T;   o_t = S^T q_t
 
-so the read-out sees the token's own write.  Around it:
+where o_t is read after token t has been written.  Around it:
 
 * q = W_q h and k = W_k h ([kv_heads, dim]; head h reads kv head h // (heads / kv_heads)), v = W_v h ([heads, vdim]);
   each passes a short causal convolution per channel (``conv`` taps, the last one the current token's, zeros before

@@ -489,12 +489,12 @@ def test_passes_smaller_than_a_prompt(name, dtype):
 
 @pytest.mark.parametrize("name, dtype", CASES)
 def test_unequal_batches_with_slots_and_pages_used_again(name, dtype):
-    """Three rounds on one engine.  Each: unequal prompts in one batch (one of a single token), then decoded together
-    while the shorter requests end earlier; the slots, state rows and pages of a round are used again by the next."""
+    """Three turns on one engine.  Each: unequal prompts in one batch (one of a single token), then decoded together
+    while the shorter requests end earlier; the slots, state rows and pages of a turn are used again by the next."""
     engine = engine_of(name, dtype, peaky=True, max_tokens=640)
-    for round_ in range(3):
-        lengths = [(1, 5), (70, 9), (33, 2), (129, 12)][round_ % 2:][:3]
-        requests = [tokens_of(name, prompt + decoded, 10 * round_ + i) for i, (prompt, decoded) in enumerate(lengths)]
+    for turn in range(3):
+        lengths = [(1, 5), (70, 9), (33, 2), (129, 12)][turn % 2:][:3]
+        requests = [tokens_of(name, prompt + decoded, 10 * turn + i) for i, (prompt, decoded) in enumerate(lengths)]
         slots = [engine.new_sequence() for _ in requests]
         got = [[] for _ in requests]
         logits = engine.step([StepEntry(slot, req[:prompt], list(range(prompt))) for slot, req, (prompt, _) in zip(slots, requests, lengths)]).cpu()
@@ -511,7 +511,7 @@ def test_unequal_batches_with_slots_and_pages_used_again(name, dtype):
                 if step == d - 1:
                     engine.release(slots[i])
         for i, req in enumerate(requests):
-            close(torch.cat(got[i]), oracle(name, dtype, True, tuple(req)), dtype, f"{name} round {round_} request {i}", model_rows=True)
+            close(torch.cat(got[i]), oracle(name, dtype, True, tuple(req)), dtype, f"{name} turn {turn} request {i}", model_rows=True)
     engine.check_kernels()
 
 
