@@ -36,6 +36,19 @@ struct PrepareParams {
 };
 
 __device__ __forceinline__ float sigmoidf(float z) { return 1.f / (1.f + expf(-z)); }
+
+// The sum of split-K partial sums in their order, eight loads in flight at a time.
+__device__ __forceinline__ float sum_splits(const float* __restrict__ base, size_t index, int n_splits, size_t split_stride) {
+    float acc = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = s0 + j < n_splits ? base[index + (size_t)(s0 + j) * split_stride] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += v[j];
+    }
+    return acc;
+}
 __device__ __forceinline__ float softplusf(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 // One warp per (token, item): items 0 .. kv_heads - 1 are the q heads, the next kv_heads the k heads, the next `heads`
@@ -52,7 +65,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const PrepareParams 
     const int channels = 2 * p.kv_heads * p.dim + p.heads * p.vdim;
     if (item == items - 1) {
         for (int h = lane; h < p.heads; h += 32)
-            p.beta[(size_t)t * p.heads + h] = sigmoidf(load_sum(p.proj, row + channels + h, p.n_splits, p.split_stride));
+            p.beta[(size_t)t * p.heads + h] = sigmoidf(sum_splits(p.proj, row + channels + h, p.n_splits, p.split_stride));
         return;
     }
     const int seq = p.token_seq[t];
@@ -79,7 +92,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const PrepareParams 
                 x[j] = w[j] = 0.f;
                 if (back < p.n_taps) {
                     w[j] = taps[(size_t)c * p.n_taps + p.n_taps - 1 - back];
-                    if (back <= local) x[j] = load_sum(proj, row - (size_t)back * p.proj_cols + c, p.n_splits, p.split_stride);
+                    if (back <= local) x[j] = sum_splits(proj, row - (size_t)back * p.proj_cols + c, p.n_splits, p.split_stride);
                     else x[j] = kept[(size_t)(p.n_taps - 1 - (back - local)) * channels + c];
                 }
             }
@@ -113,7 +126,7 @@ __global__ void conv_keep_kernel(const float* __restrict__ proj, int n_splits, s
     const int rows = n_taps - 1;
     for (int j = 0; j < rows; ++j) {
         const int from = count - rows + j;                       // index among the step's tokens; negative: an older position
-        value[j] = from >= 0 ? load_sum(proj, (size_t)(row0 + from) * proj_cols + c, n_splits, split_stride)
+        value[j] = from >= 0 ? sum_splits(proj, (size_t)(row0 + from) * proj_cols + c, n_splits, split_stride)
                              : mine[(size_t)(rows + from) * channels];
     }
     for (int j = 0; j < rows; ++j) mine[(size_t)j * channels] = value[j];
@@ -135,7 +148,7 @@ __global__ void __launch_bounds__(256) lowrank_kernel(const float* __restrict__ 
     const int count = min(LR_TOKENS, n_tokens - t0);
     for (int i = threadIdx.x; i < LR_TOKENS * rank; i += blockDim.x) {
         const int tt = i / rank, r = i % rank;
-        xs[i] = tt < count ? load_sum(proj, (size_t)(t0 + tt) * proj_cols + x_offset + r, n_splits, split_stride) : 0.f;
+        xs[i] = tt < count ? sum_splits(proj, (size_t)(t0 + tt) * proj_cols + x_offset + r, n_splits, split_stride) : 0.f;
     }
     __syncthreads();
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
@@ -162,6 +175,55 @@ __global__ void __launch_bounds__(256) lowrank_kernel(const float* __restrict__ 
         if (tt >= count) break;
         const float z = acc[tt] + b;
         out[(size_t)(t0 + tt) * n_out + n] = MODE == LR_DECAY ? -rate * softplusf(z) : sigmoidf(z);     // the decay's logarithm
+    }
+}
+
+// The same for a step of few tokens (one tile of them): 64 outputs per block, so that many SMs get one, and the
+// columns cut into four ranges, one per 64 threads, whose sums meet in shared memory.
+template <int MODE>
+__global__ void __launch_bounds__(256) lowrank_few_kernel(const float* __restrict__ proj, int n_splits, size_t split_stride, int proj_cols,
+                                                          int x_offset, int rank, const float* __restrict__ w, const float* __restrict__ bias,
+                                                          const float* __restrict__ rate_log, int per_rate, float* __restrict__ out,
+                                                          int n_tokens, int n_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float xs[];                                 // [LR_TOKENS][rank], then [4][LR_TOKENS][64] partial sums
+    float* part = xs + LR_TOKENS * rank;
+    for (int i = threadIdx.x; i < LR_TOKENS * rank; i += blockDim.x) {
+        const int tt = i / rank, r = i % rank;
+        xs[i] = tt < n_tokens ? sum_splits(proj, (size_t)tt * proj_cols + x_offset + r, n_splits, split_stride) : 0.f;
+    }
+    __syncthreads();
+    const int local = threadIdx.x & 63, slice = threadIdx.x >> 6;
+    const int n = blockIdx.x * 64 + local;
+    const int per = (rank + 3) / 4, r_begin = slice * per, r_end = min(rank, r_begin + per);
+    float acc[LR_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < LR_TOKENS; ++tt) acc[tt] = 0.f;
+    if (n < n_out) {
+        for (int r0 = r_begin; r0 < r_end; r0 += 8) {
+            float wv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wv[j] = r0 + j < r_end ? w[(size_t)(r0 + j) * n_out + n] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (r0 + j < r_end) {
+#pragma unroll
+                    for (int tt = 0; tt < LR_TOKENS; ++tt) acc[tt] += wv[j] * xs[tt * rank + r0 + j];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < LR_TOKENS; ++tt) part[(slice * LR_TOKENS + tt) * 64 + local] = acc[tt];
+    __syncthreads();
+    if (n >= n_out) return;
+    const float b = bias ? bias[n] : 0.f;
+    const float rate = MODE == LR_DECAY ? expf(rate_log[n / per_rate]) : 0.f;
+    for (int tt = slice; tt < n_tokens; tt += 4) {                 // the four ranges' sums in their order
+        const float z = part[(0 * LR_TOKENS + tt) * 64 + local] + part[(1 * LR_TOKENS + tt) * 64 + local] +
+                        part[(2 * LR_TOKENS + tt) * 64 + local] + part[(3 * LR_TOKENS + tt) * 64 + local] + b;
+        out[(size_t)tt * n_out + n] = MODE == LR_DECAY ? -rate * softplusf(z) : sigmoidf(z);
     }
 }
 
@@ -662,8 +724,21 @@ extern "C" int qt_lowrank(const float* proj, int n_splits, long long split_strid
     QT_REQUIRE((size_t)LR_TOKENS * rank * sizeof(float) <= 48 * 1024, "lowrank: %d columns are too many for a tile in shared memory", rank);
     if (n_tokens == 0) return QT_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    // few tokens: blocks of 64 outputs, so that the one tile of tokens still gives many SMs a block
-    const int threads = n_tokens <= LR_TOKENS ? 64 : 256;
+    if (n_tokens <= LR_TOKENS) {
+        const size_t few_smem = ((size_t)LR_TOKENS * rank + 4 * LR_TOKENS * 64) * sizeof(float);
+        if (few_smem <= 48 * 1024) {
+            const dim3 few_grid((n_out + 63) / 64);
+            if (mode == LR_DECAY)
+                launch_kernel(lowrank_few_kernel<LR_DECAY>, few_grid, dim3(256), few_smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset,
+                              rank, w, bias, rate_log, per_rate, out, n_tokens, n_out);
+            else
+                launch_kernel(lowrank_few_kernel<LR_SIGMOID>, few_grid, dim3(256), few_smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset,
+                              rank, w, bias, rate_log, per_rate, out, n_tokens, n_out);
+            QT_CHECK_LAUNCH("lowrank");
+            return QT_OK;
+        }
+    }
+    const int threads = 256;
     const dim3 grid((n_out + threads - 1) / threads, (n_tokens + LR_TOKENS - 1) / LR_TOKENS);
     const size_t smem = (size_t)LR_TOKENS * rank * sizeof(float);
     if (mode == LR_DECAY)

@@ -407,7 +407,15 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
         const size_t from = (size_t)t * cols + (size_t)(p.nq + p.nkv) * p.d + (size_t)vh * p.dv;
         const int* table = p.block_table + (size_t)p.token_seq[t] * p.max_blocks;
         TO* dst = (TO*)p.v_cache + cache_offset(table, p.token_pos[t], p.ring_tokens, p.page_tokens, p.nv, vh, p.dv);
-        for (int i = lane; i < p.dv; i += 32) dst[i] = from_float<TO>(load_sum((const TI*)p.qkv, from + i, p.n_splits, p.split_stride));
+        const TI* src = (const TI*)p.qkv;
+        for (int i0 = lane; i0 < p.dv; i0 += 128) {                 // four elements' loads ahead of their stores
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = i0 + 32 * j < p.dv ? load_sum(src, from + i0 + 32 * j, p.n_splits, p.split_stride) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i0 + 32 * j < p.dv) dst[i0 + 32 * j] = from_float<TO>(v[j]);
+        }
         return;
     }
     float* vec = smem + warp * p.d;
@@ -630,7 +638,8 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     const size_t smem = (size_t)warps * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     // 16-byte loads and stores need head_dim % 8 == 0 (bfloat16 rows of the cache and of q) and aligned bases
-    const bool vec = !own_values && d % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+    // (q and k heads of a projection whose values have their own shape take them too, if the values' columns keep the rows aligned)
+    const bool vec = (!own_values || (nv * dv) % 8 == 0) && d % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
                      (!write_kv || (((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0)));
     // the register form: all dimensions rotate, half a head is one or two rounds of 32 or 64 elements, enough tokens
     // to fill the machine with a few heads per warp

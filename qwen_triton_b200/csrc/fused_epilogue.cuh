@@ -34,6 +34,7 @@ struct EpilogueParams {
     const float* sq_in; int sq_tiles; float inv_hidden; float eps;
     // STORE / SWIGLU
     void* out; int out_is_float; int act;      // act: the gate's activation, QT_ACT_*
+    float limit;                               // of the capped gate (QT_ACT_CAPPED)
     // RESIDUAL
     float* residual; const float* norm_w; __nv_bfloat16* xw; float* sq_out;
     // QKV
@@ -114,7 +115,7 @@ __device__ __forceinline__ void finish_swiglu(const EpilogueParams& p, const Ope
     g.x *= ops.scale; g.y *= ops.scale; u.x *= ops.scale; u.y *= ops.scale;
     const int features = p.N >> 1, feature = w_tile * (TILE / 2) + 2 * lane;
     if (feature < features) {
-        const float a0 = gate_activation<true>(g.x, p.act) * u.x, a1 = gate_activation<true>(g.y, p.act) * u.y;
+        const float a0 = gated_value<true>(g.x, u.x, p.act, p.limit), a1 = gated_value<true>(g.y, u.y, p.act, p.limit);
         *reinterpret_cast<uint32_t*>((__nv_bfloat16*)p.out + (size_t)m * features + feature) = pack2(a0, a1);
     }
 }
@@ -200,7 +201,7 @@ inline int check_epilogue(const char* who, int epilogue, const EpilogueParams& p
             break;
         case EPI_SWIGLU:
             QT_REQUIRE(p.out != nullptr && out_dtype == QT_BF16 && p.N % 32 == 0 && (uintptr_t)p.out % 4 == 0, "%s: the gated epilogue writes bfloat16 and needs gate and up rows in groups of 16 (N=%d)", who, p.N);
-            QT_REQUIRE(p.act >= 0 && p.act < QT_ACT_COUNT, "%s: unknown activation code %d", who, p.act);
+            QT_REQUIRE(p.act >= 0 && p.act <= QT_ACT_CAPPED, "%s: unknown activation code %d", who, p.act);
             break;
         case EPI_QKV:
             QT_REQUIRE(p.d >= 16 && TILE % p.d == 0 && p.d % 4 == 0 && p.N % p.d == 0, "%s: head_dim=%d must divide %d for the fused rotation (N=%d)", who, p.d, TILE, p.N);

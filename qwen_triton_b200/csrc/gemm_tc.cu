@@ -49,7 +49,7 @@ template <int BX, typename TO, bool GATED>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
                                                           int M, int N, int kb_total, int kb_per_split,
-                                                          size_t split_stride, int stages, int act, int* status) {
+                                                          size_t split_stride, int stages, int act, float limit, int* status) {
     constexpr uint32_t X_BYTES = BX * BK * 2;
     constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr uint32_t TMEM_COLS = BX < 32 ? 32 : BX;
@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                         const float g = upper ? got : mine0;          // lower lanes: token j (their gate, the partner's up)
                         const float u = upper ? mine1 : got;          // upper lanes: token j + 1 (the partner's gate, their up)
                         const int m = x0 + c + j + (upper ? 1 : 0);
-                        if (feature < features && m < M) dst[(size_t)m * features + feature] = from_float<TO>(gate_activation<true>(g, act) * u);
+                        if (feature < features && m < M) dst[(size_t)m * features + feature] = from_float<TO>(gated_value<true>(g, u, act, limit));
                     }
                 } else if (n < N) {
 #pragma unroll
@@ -323,7 +323,7 @@ template <typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                   const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
                                                                   int M, int N, int kb_total, int kb_per_split, int splits,
-                                                                  size_t split_stride, int act, int vector_stores, int tail_tiles,
+                                                                  size_t split_stride, int act, float limit, int vector_stores, int tail_tiles,
                                                                   float* __restrict__ tail_scratch, int* tail_flags, int* status) {
     // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N = 256 weight rows, M = 256 tokens over the pair
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PAIR_W >> 3) << 17) | ((uint32_t)(PAIR_X >> 4) << 24);
@@ -542,7 +542,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
                         float f[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            f[j] = gate_activation<true>(__uint_as_float(v[8 * h + j]), act) * __uint_as_float(v[16 + 8 * h + j]);
+                            f[j] = gated_value<true>(__uint_as_float(v[8 * h + j]), __uint_as_float(v[16 + 8 * h + j]), act, limit);
                         if (vector_stores && f0 + 8 * h + 8 <= features) {
                             store8<TO>(dst + 8 * h, f);
                         } else {
@@ -616,7 +616,7 @@ int pick_tail_tiles(long long n_tiles, int pairs, int kb_total, int tail, int ta
 
 template <typename TO, bool SWIGLU>
 int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
-                size_t split_stride, int act, int tail, float* tail_scratch, int* tail_flags, int tail_pairs, int* status,
+                size_t split_stride, int act, float limit, int tail, float* tail_scratch, int* tail_flags, int tail_pairs, int* status,
                 cudaStream_t stream) {
     const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + (2 * PAIR_STAGES + 5) * 8 + 16;
     static int resident_pairs = 0;                           // pairs the device runs at once (one per TPC that can host a cluster)
@@ -649,7 +649,7 @@ int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int
     const int per16 = 16 / (int)sizeof(TO), row_elems = SWIGLU ? N / 2 : N;
     const int vector_stores = ((uintptr_t)out % 16 == 0 && row_elems % per16 == 0 && split_stride % per16 == 0) ? 1 : 0;
     launch_kernel_cluster(gemm_tc_pair_kernel<TO, SWIGLU>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2, map_w, map_x, out, M, N, kb_total,
-                          kb_per_split, splits, split_stride, act, vector_stores, tail_tiles, tail_scratch, tail_flags, status);
+                          kb_per_split, splits, split_stride, act, limit, vector_stores, tail_tiles, tail_scratch, tail_flags, status);
     QT_CHECK_LAUNCH("gemm_tc_pair");
     return QT_OK;
 }
@@ -657,7 +657,7 @@ int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int
 // ----------------------------------------------------------------------------- host side
 template <int BX, typename TO, bool GATED>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
-           size_t split_stride, int stages, int act, int* status, cudaStream_t stream) {
+           size_t split_stride, int stages, int act, float limit, int* status, cudaStream_t stream) {
     constexpr uint32_t STAGE_BYTES = W_BYTES + BX * BK * 2;
     // Up to 16 tokens a block streams weights through a three-stage ring (54 KB), so that four blocks share an SM and
     // the next product's blocks can move in beside this one's last blocks and fetch their first weight tiles early
@@ -682,7 +682,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, i
     }
     const int kb_per_split = (kb_total + splits - 1) / splits;
     dim3 grid(((N + BW - 1) / BW) * ((M + BX - 1) / BX), 1, splits);
-    launch_kernel(gemm_tc_kernel<BX, TO, GATED>, dim3(grid), dim3(THREADS), smem, stream, map_w, map_x, out, M, N, kb_total, kb_per_split, split_stride, stages, act, status);
+    launch_kernel(gemm_tc_kernel<BX, TO, GATED>, dim3(grid), dim3(THREADS), smem, stream, map_w, map_x, out, M, N, kb_total, kb_per_split, split_stride, stages, act, limit, status);
     QT_CHECK_LAUNCH("gemm_tc");
     return QT_OK;
 }
@@ -690,13 +690,13 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, i
 
 template <typename TO, bool GATED>
 int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
-                  size_t split_stride, int stages, int act, int* status, cudaStream_t stream) {
+                  size_t split_stride, int stages, int act, float limit, int* status, cudaStream_t stream) {
     switch (bx) {
-        case 16: return launch<16, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
-        case 32: return launch<32, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
-        case 64: return launch<64, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
-        case 128: return launch<128, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
-        case 256: return launch<256, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
+        case 16: return launch<16, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, limit, status, stream);
+        case 32: return launch<32, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, limit, status, stream);
+        case 64: return launch<64, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, limit, status, stream);
+        case 128: return launch<128, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, limit, status, stream);
+        case 256: return launch<256, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, limit, status, stream);
     }
     QT_FAIL(QT_ERR_ARG, "gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", bx);
 }
@@ -711,8 +711,8 @@ int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, TO
 // With `gated` the weight's rows alternate 16 of a gate and 16 of an up projection and `out` is [M, N / 2] bfloat16 =
 // act(gate) * up (`act`: one of QT_ACT_*; one K range only).
 extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int token_tile,
-                          int splits, long long split_stride, int stages, int gated, int act, int* status, void* stream) {
-    QT_REQUIRE(!gated || (splits == 1 && out_dtype == QT_BF16 && N % 32 == 0 && act >= 0 && act < QT_ACT_COUNT),
+                          int splits, long long split_stride, int stages, int gated, int act, float limit, int* status, void* stream) {
+    QT_REQUIRE(!gated || (splits == 1 && out_dtype == QT_BF16 && N % 32 == 0 && act >= 0 && act <= QT_ACT_CAPPED),
                "gemm_tc: the gated epilogue writes bfloat16 from one K range of gate and up rows in groups of 16 (N=%d, splits=%d)", N, splits);
     QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     QT_REQUIRE(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
@@ -731,11 +731,11 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     if (gated)
-        return dispatch_tile<__nv_bfloat16, true>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, stages, act, status, s);
+        return dispatch_tile<__nv_bfloat16, true>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, stages, act, limit, status, s);
     if (out_dtype == QT_BF16)
-        return dispatch_tile<__nv_bfloat16, false>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, splits, (size_t)split_stride, stages, 0, status, s);
+        return dispatch_tile<__nv_bfloat16, false>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, splits, (size_t)split_stride, stages, 0, 0.f, status, s);
     if (out_dtype == QT_F32)
-        return dispatch_tile<float, false>(token_tile, map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, stages, 0, status, s);
+        return dispatch_tile<float, false>(token_tile, map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, stages, 0, 0.f, status, s);
     QT_FAIL(QT_ERR_ARG, "gemm_tc: unknown output type %d", out_dtype);
 }
 
@@ -749,9 +749,9 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
 // resident pairs, or null pointers, every tile is walked whole.
 extern "C" int qt_gemm_tc_pair_slots() { return PAIR_SLOT_FLOATS; }
 extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int swiglu,
-                               int act, int splits, long long split_stride, int tail, float* tail_scratch, int* tail_flags,
+                               int act, float limit, int splits, long long split_stride, int tail, float* tail_scratch, int* tail_flags,
                                int tail_pairs, int* status, void* stream) {
-    QT_REQUIRE(act >= 0 && act < QT_ACT_COUNT, "gemm_tc_pair: unknown activation code %d", act);
+    QT_REQUIRE(act >= 0 && act <= QT_ACT_CAPPED, "gemm_tc_pair: unknown activation code %d", act);
     QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc_pair: bad sizes M=%d N=%d K=%d", M, N, K);
     QT_REQUIRE(K % 8 == 0, "gemm_tc_pair: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
     QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc_pair: operands must be 16-byte aligned");
@@ -768,9 +768,9 @@ extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_
     rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)PAIR_HALF);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == QT_BF16 && swiglu) return launch_pair<__nv_bfloat16, true>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, act, tail, tail_scratch, tail_flags, tail_pairs, status, s);
-    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16, false>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, 0, tail, tail_scratch, tail_flags, tail_pairs, status, s);
-    if (out_dtype == QT_F32 && !swiglu) return launch_pair<float, false>(map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, 0, tail, tail_scratch, tail_flags, tail_pairs, status, s);
+    if (out_dtype == QT_BF16 && swiglu) return launch_pair<__nv_bfloat16, true>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, act, limit, tail, tail_scratch, tail_flags, tail_pairs, status, s);
+    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16, false>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, 0, 0.f, tail, tail_scratch, tail_flags, tail_pairs, status, s);
+    if (out_dtype == QT_F32 && !swiglu) return launch_pair<float, false>(map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, 0, 0.f, tail, tail_scratch, tail_flags, tail_pairs, status, s);
     QT_FAIL(QT_ERR_ARG, "gemm_tc_pair: output type %d%s is not offered", out_dtype, swiglu ? " with the SiLU-gated epilogue" : "");
 }
 

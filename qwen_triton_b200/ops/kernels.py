@@ -79,15 +79,15 @@ _SIGNATURES = {
         "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "gemm_tc": {
-        "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
-        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr,
+        "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr],
+        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ll, _c_int, _c_ptr,
                             _c_ptr, _c_int, _c_ptr, _c_ptr],
         "qt_gemm_tc_pair_slots": [],
     },
     "gemm_fused": {
         "qt_gemm_fused": [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_ptr, _c_int, _c_int, _c_float,
-                          _c_ptr, _c_int, _c_int,
+                          _c_ptr, _c_int, _c_int, _c_float,
                           _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                           _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float,
                           _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
@@ -484,7 +484,7 @@ SWIGLU_GROUP = 16      # rows of gate and of up that alternate in a weight laid 
 # gate activations of a gated feed-forward, act(gate) * up: names a configuration may use -> the kernels' codes
 ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu": 2, "relu": 3}
 # a gate that also treats the up value and has a parameter ``limit``: g' = min(g, limit), u' = clamp(u, -limit, limit),
-# y = g' sigmoid(1.702 g') (u' + 1).  Taken by ``swiglu`` and the experts' kernels, not by the products' epilogues.
+# y = g' sigmoid(1.702 g') (u' + 1).  Taken, with ``limit``, by ``swiglu``, the experts' kernels and the products' gated epilogues.
 CAPPED_GATE = "capped_sigmoid"
 _CAPPED_CODE = 4
 
@@ -921,7 +921,7 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | None = None, stages: int = 0,
-            swiglu: bool = False, activation: str = "silu") -> None:
+            swiglu: bool = False, activation: str = "silu", limit: float = 0.0) -> None:
     """out = a [M, K] @ w [N, K]^T on the tcgen05 tensor cores; bfloat16 inputs, K a multiple of 8.
 
     ``out`` is [1, M, N] bfloat16 or float, or [splits, M, N] float for split-K partial sums.  With ``swiglu`` the
@@ -941,8 +941,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | No
         raise KernelError("gemm_tc: the output must be a bfloat16 or float32 CUDA tensor")
     tile = token_tile or tc_token_tile(rows)
     _call("gemm_tc", "qt_gemm_tc", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k, tile,
-          out.n_splits, out.split_stride, int(stages), 1 if swiglu else 0, activation_code(activation) if swiglu else 0,
-          _ptr(_status_word(a.device)), _stream())
+          out.n_splits, out.split_stride, int(stages), 1 if swiglu else 0, activation_code(activation, True) if swiglu else 0,
+          float(limit), _ptr(_status_word(a.device)), _stream())
 
 
 _PAIR_TAIL: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = {}
@@ -970,7 +970,7 @@ def pair_tail_mode() -> int:
 
 
 def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = False, activation: str = "silu",
-                 tail: int | None = None) -> None:
+                 tail: int | None = None, limit: float = 0.0) -> None:
     """The same product by pairs of blocks on the two SMs of a TPC (tcgen05 cta_group::2): 256 weight rows x
     256 tokens per tile, each block staging half of both operands; one persistent pair per TPC with two
     accumulators in tensor memory.  Meant for many tokens; ``out`` may be [splits, M, N] float partial sums, which
@@ -991,7 +991,7 @@ def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = 
     tail = pair_tail_mode() if tail is None else int(tail)
     slots, flags, pairs = _pair_tail(a.device) if tail != 0 and out.n_splits == 1 else (None, None, 0)
     _call("gemm_tc", "qt_gemm_tc_pair", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k,
-          1 if swiglu else 0, activation_code(activation) if swiglu else 0, out.n_splits, out.split_stride,
+          1 if swiglu else 0, activation_code(activation, True) if swiglu else 0, float(limit), out.n_splits, out.split_stride,
           tail, _ptr(slots) if slots is not None else None, _ptr(flags) if flags is not None else None, pairs,
           _ptr(_status_word(a.device)), _stream())
 
@@ -1065,7 +1065,7 @@ def fused_qkv_supported(head_dim: int, rotary_dim: int) -> bool:
 def _fused(x, w: torch.Tensor, splits: int, epilogue: int, *, out=None, residual=None, norm_w=None, xw=None, sq_out=None,
            q_out=None, k_cache=None, v_cache=None, token_seq=None, token_pos=None, block_table=None, q_w=None, k_w=None,
            qk_eps=0.0, cos_sin=None, nq=0, nkv=0, d=0, page_tokens=0, ring_tokens=0, write_kv=False, stages: int = 0,
-           act: int = 0, interleaved: bool = False) -> None:
+           act: int = 0, interleaved: bool = False, limit: float = 0.0) -> None:
     scaled = x if isinstance(x, ScaledRows) else None
     a = scaled.tensor if scaled is not None else x
     _need(a, "x", torch.bfloat16)
@@ -1083,7 +1083,7 @@ def _fused(x, w: torch.Tensor, splits: int, epilogue: int, *, out=None, residual
     _call("gemm_fused", "qt_gemm_fused", _ptr(a), _ptr(w), rows, w.shape[0], k, tc_token_tile(rows), int(splits), int(stages), epilogue,
           _ptr(scaled.sq) if scaled is not None else None, scaled.sq.shape[0] if scaled is not None else 0,
           scaled.width if scaled is not None else 0, float(scaled.eps) if scaled is not None else 0.0,
-          _ptr(out), _CODES.get(out.dtype, -1) if out is not None else 0, int(act),
+          _ptr(out), _CODES.get(out.dtype, -1) if out is not None else 0, int(act), float(limit),
           _ptr(residual), _ptr(norm_w), _ptr(xw), _ptr(sq_out),
           _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(token_seq), _ptr(token_pos), _ptr(block_table),
           block_table.shape[1] if block_table is not None else 0, _ptr(q_w), _ptr(k_w), float(qk_eps),
@@ -1115,12 +1115,13 @@ def gemm_fused_residual(x, w: torch.Tensor, residual: torch.Tensor, norm_weight:
     return ScaledRows(xw, sq, n, float(eps))
 
 
-def gemm_fused_swiglu(x, w: torch.Tensor, out: torch.Tensor, splits: int = 1, stages: int = 0, activation: str = "silu") -> None:
+def gemm_fused_swiglu(x, w: torch.Tensor, out: torch.Tensor, splits: int = 1, stages: int = 0, activation: str = "silu",
+                      limit: float = 0.0) -> None:
     """out [M, N / 2] (bfloat16) = act(gate) * up for a weight whose rows alternate SWIGLU_GROUP of gate and of up."""
     if w.shape[0] % (2 * SWIGLU_GROUP):
         raise KernelError(f"gemm_fused_swiglu: {w.shape[0]} rows are not gate and up rows in groups of {SWIGLU_GROUP}")
     _need(out, "out", torch.bfloat16, (x.shape[0], w.shape[0] // 2))
-    _fused(x, w, splits, _EPI_SWIGLU, out=out, stages=stages, act=activation_code(activation))
+    _fused(x, w, splits, _EPI_SWIGLU, out=out, stages=stages, act=activation_code(activation, True), limit=limit)
 
 
 def gemm_fused_qkv(x, w: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,

@@ -116,7 +116,7 @@ class Attention:
             self.qkv = Linear("attn.qkv" + (".biased" if self.bias else ""), proj_rows, self.hidden, runtime, role="qkv", bias=self.bias)
         self.float_out = bool(params.get("float_out", False))
         self.o = Linear("attn.o" + (".biased" if self.o_bias else "") + (".float" if self.float_out else ""), self.hidden,
-                        self.heads_out * self.dv, runtime, role="" if self.float_out else "attn_out", bias=self.o_bias, float_out=self.float_out)
+                        self.heads_out * self.dv, runtime, role="attn_out", bias=self.o_bias, float_out=self.float_out)
         ws = runtime.workspace
         ws.declare("attn.q", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
         ws.declare("attn.ctx", runtime.max_step_tokens * self.nq * self.dv, runtime.dtype)

@@ -10,7 +10,7 @@ from dataclasses import replace
 
 from ..config.spec import LayerSpec
 from ..weights.tensors import TensorSpec
-from .base import ResidualStream, Runtime, part_class, register_block
+from .base import DeferredProduct, ResidualStream, Runtime, part_class, register_block
 
 
 @register_block("pre_norm")
@@ -123,4 +123,11 @@ class ParallelBlock(PreNormBlock):
             if part is None:
                 continue
             result = part.forward(*args)
-            stream.add_beside(result.run() if hasattr(result, "run") else result)
+            if isinstance(result, DeferredProduct):
+                # few tokens: the part's last product adds itself to the float stream in its epilogue (nothing else
+                # reads the stream until the next norm; the other part reads the normed rows)
+                if result.linear.fusable(stream.residual.shape[0]):
+                    result.linear.into_residual(result.x, stream.residual)
+                    continue
+                result = result.run()
+            stream.add_beside(result)

@@ -1,7 +1,7 @@
 """Dense gated feed-forward: down(act(gate(x)) * up(x)) (qwen_triton/modules/mlp.py:10-22, where act is SiLU;
 here it is a parameter: any of ``kernels.ACTIVATIONS``, or ``kernels.CAPPED_GATE`` with ``limit``:
 g' = min(g, limit), u' = clamp(u, -limit, limit), y = g' sigmoid(1.702 g') (u' + 1), computed by the gate kernel
-behind the plain product).  ``weight_suffix`` is what the tensor names add to the projections' names (default
+in the same places as the other activations: the products' epilogues, or the gate kernel).  ``weight_suffix`` is what the tensor names add to the projections' names (default
 ".weight"); ``float_out`` makes the down projection hand on float sums.
 
 gate and up run as one product over the fused weight [gate; up].  In bfloat16 its rows alternate 16 of gate and
@@ -37,14 +37,14 @@ class GatedMLP:
         if self.capped and self.limit <= 0.0:
             raise ValueError(f"{prefix}: the capped gate needs a positive limit")
         self.names = self._names(params)
-        # the gate in a product's epilogue: the activations that are a function of the gate value alone
-        fused = runtime.dtype == torch.bfloat16 and self.inter % kernels.SWIGLU_GROUP == 0 and self.hidden % 8 == 0 and not self.capped
+        # the gate in a product's epilogue: its rows then alternate 16 of gate and 16 of up
+        fused = runtime.dtype == torch.bfloat16 and self.inter % kernels.SWIGLU_GROUP == 0 and self.hidden % 8 == 0
         self.group = kernels.SWIGLU_GROUP if fused else 0
         float_out = bool(params.get("float_out", False))
         key = str(params.get("buffers", "mlp"))           # several such parts in one layer keep their buffers apart
         self.gate_up = Linear(f"{key}.gate_up", 2 * self.inter, self.hidden, runtime, role="gate" if fused else "")
         self.down = Linear(f"{key}.down" + (".float" if float_out else ""), self.hidden, self.inter, runtime,
-                           role="" if float_out else "mlp_out", float_out=float_out)
+                           role="mlp_out", float_out=float_out)
         self.act_buffer = f"{key}.act"
         runtime.workspace.declare(self.act_buffer, runtime.max_step_tokens * self.inter, runtime.dtype)
         # few tokens: the gate in the epilogue of the gate/up product, which then also applies the factor of the norm
@@ -75,12 +75,14 @@ class GatedMLP:
         tokens = x.shape[0]
         act = self.runtime.workspace.view(self.act_buffer, tokens, self.inter)
         if self.takes_scaled_rows and self.gate_up.fusable(tokens):
-            self.gate_up.into_swiglu(x, act, self.activation)
+            self.gate_up.into_swiglu(x, act, self.activation, self.limit)
         elif self.group and kernels.gemm_uses_pairs(x, self.gate_up.weight):
-            kernels.gemm_tc_pair(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation)
+            kernels.gemm_tc_pair(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation,
+                                 limit=self.limit)
         elif self.group and kernels.gemm_tc_supported(x, self.gate_up.weight) and self.gate_up.plan_splits(tokens) == 1:
             # a weight whose tiles fill the machine unsplit: the gate in the plain product's epilogue
-            kernels.gemm_tc(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation)
+            kernels.gemm_tc(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation,
+                            limit=self.limit)
         else:
             kernels.swiglu(self.gate_up(x), act, self.group, self.activation, self.limit)
         # few tokens: the down projection is left to the norm behind it, which launches it with the residual addition

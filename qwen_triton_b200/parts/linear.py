@@ -190,9 +190,9 @@ class Linear:
         """residual += x W^T, and the norm behind it prepared (see ``kernels.gemm_fused_residual``)."""
         return kernels.gemm_fused_residual(x, self.weight, residual, norm_weight, eps, xw, sq, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(x.shape[0]))
 
-    def into_swiglu(self, x, out: torch.Tensor, activation: str = "silu") -> None:
+    def into_swiglu(self, x, out: torch.Tensor, activation: str = "silu", limit: float = 0.0) -> None:
         kernels.gemm_fused_swiglu(x, self.weight, out, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(x.shape[0]),
-                                  activation=activation)
+                                  activation=activation, limit=limit)
 
     def into_qkv(self, x, *args, **kwargs) -> None:
         kernels.gemm_fused_qkv(x, self.weight, *args, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(x.shape[0]), **kwargs)

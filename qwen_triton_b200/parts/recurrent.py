@@ -32,7 +32,7 @@ import torch
 
 from ..ops import kernels
 from ..weights.tensors import TensorSpec
-from .base import Runtime, StateRequest, register_mixer, to_device
+from .base import DeferredProduct, Runtime, StateRequest, register_mixer, to_device
 from .linear import Linear
 
 _UNIT_EPS = 1e-6      # inside the root of the unit norms of q and k
@@ -70,7 +70,7 @@ class GatedDeltaRule:
         self.proj_rows = -(-used // 8) * 8
         self.proj = Linear("delta.proj", self.proj_rows, self.hidden, runtime, float_out=True)
         float_out = bool(params.get("float_out", False))
-        self.o = Linear("delta.o" + (".float" if float_out else ""), self.hidden, self.heads * self.vdim, runtime, float_out=float_out)
+        self.o = Linear("delta.o" + (".float" if float_out else ""), self.hidden, self.heads * self.vdim, runtime, float_out=float_out, role="attn_out")
         ws = runtime.workspace
         tokens = runtime.max_step_tokens
         for name, width in (("delta.q", self.kv_heads * self.dim), ("delta.k", self.kv_heads * self.dim), ("delta.v", self.heads * self.vdim),
@@ -169,4 +169,6 @@ class GatedDeltaRule:
             kernels.delta_scan(q, k, v, beta, decay, states.state, read, ctx)
         normed = ws.view("delta.normed", tokens, self.heads, self.vdim)
         kernels.gated_head_norm(read, gate, self.norm, self.eps, normed)
-        return self.o(normed.view(tokens, self.heads * self.vdim))
+        normed = normed.view(tokens, self.heads * self.vdim)
+        # few tokens: the product is left to the block, which launches it with the residual addition in its epilogue
+        return DeferredProduct(self.o, normed) if self.o.fusable(tokens) else self.o(normed)

@@ -488,6 +488,22 @@ def test_passes_smaller_than_a_prompt(name, dtype):
 
 
 @pytest.mark.parametrize("name, dtype", CASES)
+def test_a_prompt_of_more_than_256_tokens(name, dtype):
+    """Beyond 256 rows the products run by block pairs (the gate in their epilogue), the experts in tiles, the
+    recurrence in 19 chunks; then four one-token steps, whose products end in the cluster's epilogues."""
+    engine = engine_of(name, dtype, peaky=True)
+    tokens = tokens_of(name, 304, 8)
+    want = oracle(name, dtype, True, tuple(tokens))
+    slot = engine.new_sequence()
+    got = [engine.step([StepEntry(slot, tokens[:300], list(range(300)))]).cpu()]
+    for t in range(300, 304):
+        got.append(engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu())
+    engine.release(slot)
+    close(torch.cat(got), want, dtype, f"{name} 300 tokens and four more", model_rows=True)
+    engine.check_kernels()
+
+
+@pytest.mark.parametrize("name, dtype", CASES)
 def test_unequal_batches_with_slots_and_pages_used_again(name, dtype):
     """Three turns on one engine.  Each: unequal prompts in one batch (one of a single token), then decoded together
     while the shorter requests end earlier; the slots, state rows and pages of a turn are used again by the next."""
