@@ -12,8 +12,9 @@
 //   conv_keep_kernel       the last taps - 1 raw inputs of every sequence, kept for its next step
 //   lowrank_kernel         y = f(W2 (x) + bias) for a projection through a few columns (x is a slice of the first
 //                          projection's output): f = -exp(rate_h) softplus(.), the logarithm of the decays, or sigmoid for a gate
-//   delta_scan_kernel      the recurrence token by token (steps of few tokens per sequence: a state is read and written once
-//                          per token anyway)
+//   delta_step_kernel      the recurrence token by token (steps of few tokens per sequence: a state is read and written once
+//                          per step anyway, and the kernel is laid out for those bytes); delta_scan_kernel is an older
+//                          form of it (QT_B200_DELTA_STEP=0), a column's rows over 8 lanes
 //   delta_chunk_prepare_kernel, delta_chunk_scan_kernel
 //                          the same recurrence in chunks of 16 tokens for longer steps (see there)
 //   gated_head_norm_kernel o / rms(o) * w * gate per head, into the element type of the output projection's input
@@ -178,7 +179,7 @@ __global__ void __launch_bounds__(256) lowrank_kernel(const float* __restrict__ 
     }
 }
 
-// The same for a step of few tokens (one tile of them): 64 outputs per block, so that many SMs get one, and the
+// The same for a step of few tokens (up to 16 tiles of them): 64 outputs per block, so that many SMs get one, and the
 // columns cut into four ranges, one per 64 threads, whose sums meet in shared memory.
 template <int MODE>
 __global__ void __launch_bounds__(256) lowrank_few_kernel(const float* __restrict__ proj, int n_splits, size_t split_stride, int proj_cols,
@@ -189,9 +190,12 @@ __global__ void __launch_bounds__(256) lowrank_few_kernel(const float* __restric
     pdl_wait();
     extern __shared__ float xs[];                                 // [LR_TOKENS][rank], then [4][LR_TOKENS][64] partial sums
     float* part = xs + LR_TOKENS * rank;
+    const int t0 = blockIdx.y * LR_TOKENS;
+    n_tokens = min(LR_TOKENS, n_tokens - t0);                     // of this tile
+    out += (size_t)t0 * n_out;
     for (int i = threadIdx.x; i < LR_TOKENS * rank; i += blockDim.x) {
         const int tt = i / rank, r = i % rank;
-        xs[i] = tt < n_tokens ? sum_splits(proj, (size_t)tt * proj_cols + x_offset + r, n_splits, split_stride) : 0.f;
+        xs[i] = tt < n_tokens ? sum_splits(proj, (size_t)(t0 + tt) * proj_cols + x_offset + r, n_splits, split_stride) : 0.f;
     }
     __syncthreads();
     const int local = threadIdx.x & 63, slice = threadIdx.x >> 6;
@@ -563,17 +567,19 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int RQ>
-__global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(const ChunkScanParams p) {
+// LPC lanes per column: 16 as described, or 32 (a warp per column, dim a multiple of 128: twice the warps, each with half
+// the rows; lanes l and l + 16 then both carry token l's scalars).
+template <int LPC, int RQ>
+__global__ void __launch_bounds__(FAST_COLS * LPC) delta_chunk_scan_fast_kernel(const ChunkScanParams p) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    constexpr int DIM = 64 * RQ;
+    constexpr int DIM = 4 * LPC * RQ;
     constexpr int PER_TOKEN = 3 * DIM + AB + FAST_COLS;           // kt, qt, kb rows, the token's row of `ab` (with beta), v columns
     constexpr int PER_CHUNK = CH * PER_TOKEN + DIM;
     float* buffers[2] = {sm, sm + PER_CHUNK};
     const int vdim = p.vdim, head = blockIdx.y, seq = blockIdx.z;
-    const int lane = threadIdx.x & 31, l = threadIdx.x & 15, col = threadIdx.x >> 4;
+    const int lane = threadIdx.x & 31, row_lane = threadIdx.x & (LPC - 1), l = threadIdx.x & 15, col = threadIdx.x / LPC;
     const int j = blockIdx.x * FAST_COLS + col;
     const int row0 = p.seq_start[seq], count = p.seq_start[seq + 1] - row0;
     float* state = p.state + ((size_t)p.slots[seq] * p.heads + head) * DIM * vdim;
@@ -582,7 +588,7 @@ __global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(c
 #pragma unroll
     for (int q = 0; q < RQ; ++q)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s[q][e] = state[(size_t)(4 * (l + 16 * q) + e) * vdim + j];
+        for (int e = 0; e < 4; ++e) s[q][e] = state[(size_t)(4 * (row_lane + LPC * q) + e) * vdim + j];
 
     auto fetch = [&](int chunk, float* buf) {
         const int first = chunk * CH, n = min(CH, count - first);
@@ -617,15 +623,22 @@ __global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(c
             float a = 0.f, b = 0.f;
 #pragma unroll
             for (int q = 0; q < RQ; ++q) {
-                const float4 kt = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + 4 * (l + 16 * q));
-                const float4 qt = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + DIM + 4 * (l + 16 * q));
+                const float4 kt = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + 4 * (row_lane + LPC * q));
+                const float4 qt = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + DIM + 4 * (row_lane + LPC * q));
                 a += kt.x * s[q][0] + kt.y * s[q][1] + kt.z * s[q][2] + kt.w * s[q][3];
                 b += qt.x * s[q][0] + qt.y * s[q][1] + qt.z * s[q][2] + qt.w * s[q][3];
             }
             pred[tt] = a;
             read[tt] = b;
         }
-        // sums over the 16 lanes of the column, token l's landing in lane l: halve the tokens a lane carries four times
+        // sums over the lanes of the column, token l's landing in lane l: halve the tokens a lane carries four times
+        if (LPC == 32) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) {
+                pred[tt] += __shfl_xor_sync(0xffffffffu, pred[tt], 16);
+                read[tt] += __shfl_xor_sync(0xffffffffu, read[tt], 16);
+            }
+        }
 #pragma unroll
         for (int step = 8; step >= 1; step >>= 1) {
             const bool upper = (l & step) != 0;
@@ -645,21 +658,21 @@ __global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(c
 #pragma unroll
         for (int tt = 0; tt < CH; ++tt) {
             const float candidate = beta * (vj - mine_p);                       // u of this lane's token, final once tt reaches it
-            u[tt] = __shfl_sync(0xffffffffu, candidate, (lane & 16) + tt);
+            u[tt] = __shfl_sync(0xffffffffu, candidate, LPC == 32 ? tt : (lane & 16) + tt);
             const float* column = buf + tt * PER_TOKEN + 3 * DIM;              // what u_tt adds to the later tokens
             mine_p += column[l] * u[tt];                                        // zero unless l > tt
             mine_r += column[CH + l] * u[tt];                                   // zero unless l >= tt
         }
-        if (l < n) p.out[((size_t)(row0 + chunk * CH + l) * p.heads + head) * vdim + j] = mine_r;
+        if (row_lane < n) p.out[((size_t)(row0 + chunk * CH + l) * p.heads + head) * vdim + j] = mine_r;
         // the state behind the chunk
         const float* gc = buf + CH * PER_TOKEN;
 #pragma unroll
         for (int q = 0; q < RQ; ++q) {
-            const float4 g = *reinterpret_cast<const float4*>(gc + 4 * (l + 16 * q));
+            const float4 g = *reinterpret_cast<const float4*>(gc + 4 * (row_lane + LPC * q));
             float acc[4] = {g.x * s[q][0], g.y * s[q][1], g.z * s[q][2], g.w * s[q][3]};
 #pragma unroll
             for (int tt = 0; tt < CH; ++tt) {
-                const float4 kb = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + 2 * DIM + 4 * (l + 16 * q));
+                const float4 kb = *reinterpret_cast<const float4*>(buf + tt * PER_TOKEN + 2 * DIM + 4 * (row_lane + LPC * q));
                 acc[0] += kb.x * u[tt]; acc[1] += kb.y * u[tt]; acc[2] += kb.z * u[tt]; acc[3] += kb.w * u[tt];
             }
 #pragma unroll
@@ -669,7 +682,7 @@ __global__ void __launch_bounds__(FAST_COLS * CH) delta_chunk_scan_fast_kernel(c
 #pragma unroll
     for (int q = 0; q < RQ; ++q)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) state[(size_t)(4 * (l + 16 * q) + e) * vdim + j] = s[q][e];
+        for (int e = 0; e < 4; ++e) state[(size_t)(4 * (row_lane + LPC * q) + e) * vdim + j] = s[q][e];
 }
 
 // out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * gate[t, h, :].  One warp per (token, head).
@@ -688,6 +701,90 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float* __res
     const float inv = rsqrtf(warp_sum(sq) / (float)vdim + eps);
     for (int i = lane; i < vdim; i += 32)
         out[item * vdim + i] = from_float<TO>(src[i] * inv * w[i] * (gate ? gate[item * vdim + i] : 1.f));
+}
+
+// ----------------------------------------------------------------------------- the recurrence, few tokens per sequence
+// A step of one token (or a few) per sequence costs the state's bytes, so the kernel is laid out for them: a block
+// owns STEP_COLS = 32 neighbouring columns of one head's state and threadIdx.x = row group * 32 + column, so a warp reads
+// and writes 128 consecutive bytes of a row; a thread keeps RPT consecutive rows of its column in registers, and the
+// two sums over rows (the prediction, the read-out) meet in shared memory.  grid (column blocks, heads, sequences).
+constexpr int STEP_COLS = 32;
+
+template <int RPT>
+__global__ void __launch_bounds__(512) delta_step_kernel(const ScanParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int dim = p.dim, vdim = p.vdim;
+    const int groups = blockDim.x / STEP_COLS;
+    float* ks = sm;                     // [dim]
+    float* qs = ks + dim;               // [dim]
+    float* gs = qs + dim;               // [dim] decays
+    float* sums = gs + dim;             // [groups][STEP_COLS]
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int kvh = head / (p.heads / p.kv_heads);
+    const int c = threadIdx.x % STEP_COLS, rg = threadIdx.x / STEP_COLS;
+    const int j = blockIdx.x * STEP_COLS + c;
+    const bool live = j < vdim;
+    const int row0 = p.seq_start[seq], count = p.seq_start[seq + 1] - row0;
+    float* state = p.state + ((size_t)p.slots[seq] * p.heads + head) * dim * vdim;
+    float s[RPT];
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) {
+        const int i = rg * RPT + m;
+        s[m] = (live && i < dim) ? state[(size_t)i * vdim + j] : 0.f;
+    }
+    for (int tt = 0; tt < count; ++tt) {
+        const size_t t = (size_t)(row0 + tt);
+        __syncthreads();                                              // everyone is done with the token before
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+            ks[i] = p.k[(t * p.kv_heads + kvh) * dim + i];
+            qs[i] = p.q[(t * p.kv_heads + kvh) * dim + i];
+            gs[i] = expf(p.decay[(t * p.heads + head) * dim + i]);
+        }
+        const float vj = live ? p.v[(t * p.heads + head) * vdim + j] : 0.f;
+        const float beta = p.beta[t * p.heads + head];
+        __syncthreads();
+        float part = 0.f;
+#pragma unroll
+        for (int m = 0; m < RPT; ++m) {
+            const int i = rg * RPT + m;
+            if (i < dim) { s[m] *= gs[i]; part += s[m] * ks[i]; }
+        }
+        sums[rg * STEP_COLS + c] = part;
+        __syncthreads();
+        float pred = 0.f;
+        for (int g = 0; g < groups; ++g) pred += sums[g * STEP_COLS + c];
+        const float u = beta * (vj - pred);
+        part = 0.f;
+#pragma unroll
+        for (int m = 0; m < RPT; ++m) {
+            const int i = rg * RPT + m;
+            if (i < dim) { s[m] += ks[i] * u; part += s[m] * qs[i]; }
+        }
+        __syncthreads();                                              // the predictions have been read
+        sums[rg * STEP_COLS + c] = part;
+        __syncthreads();
+        if (rg == 0 && live) {
+            float o = 0.f;
+            for (int g = 0; g < groups; ++g) o += sums[g * STEP_COLS + c];
+            p.out[(t * p.heads + head) * vdim + j] = o;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) {
+        const int i = rg * RPT + m;
+        if (live && i < dim) state[(size_t)i * vdim + j] = s[m];
+    }
+}
+
+template <int RPT>
+static int launch_step(const ScanParams& p, int n_seqs, cudaStream_t s) {
+    const int groups = (p.dim + RPT - 1) / RPT;
+    const size_t smem = ((size_t)3 * p.dim + (size_t)groups * STEP_COLS) * sizeof(float);
+    launch_kernel(delta_step_kernel<RPT>, dim3((p.vdim + STEP_COLS - 1) / STEP_COLS, p.heads, n_seqs), dim3(groups * STEP_COLS), smem, s, p);
+    QT_CHECK_LAUNCH("delta_step");
+    return QT_OK;
 }
 
 // ----------------------------------------------------------------------------- entry points
@@ -724,10 +821,10 @@ extern "C" int qt_lowrank(const float* proj, int n_splits, long long split_strid
     QT_REQUIRE((size_t)LR_TOKENS * rank * sizeof(float) <= 48 * 1024, "lowrank: %d columns are too many for a tile in shared memory", rank);
     if (n_tokens == 0) return QT_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    if (n_tokens <= LR_TOKENS) {
+    if (n_tokens <= 16 * LR_TOKENS) {
         const size_t few_smem = ((size_t)LR_TOKENS * rank + 4 * LR_TOKENS * 64) * sizeof(float);
         if (few_smem <= 48 * 1024) {
-            const dim3 few_grid((n_out + 63) / 64);
+            const dim3 few_grid((n_out + 63) / 64, (n_tokens + LR_TOKENS - 1) / LR_TOKENS);
             if (mode == LR_DECAY)
                 launch_kernel(lowrank_few_kernel<LR_DECAY>, few_grid, dim3(256), few_smem, s, proj, n_splits, (size_t)split_stride, proj_cols, x_offset,
                               rank, w, bias, rate_log, per_rate, out, n_tokens, n_out);
@@ -774,6 +871,12 @@ extern "C" int qt_delta_scan(const float* q, const float* k, const float* v, con
     if (n_seqs == 0) return QT_OK;
     ScanParams p{q, k, v, beta, decay, state, out, seq_start, slots, heads, kv_heads, dim, vdim};
     cudaStream_t s = (cudaStream_t)stream;
+    static const bool lanes_form = [] { const char* env = getenv("QT_B200_DELTA_STEP"); return env && env[0] == '0'; }();
+    if (!lanes_form) {                                                // rows of a column over row groups, 128 bytes of a row per warp
+        if (dim <= 64) return launch_step<8>(p, n_seqs, s);
+        if (dim <= 256) return launch_step<16>(p, n_seqs, s);
+        return launch_step<32>(p, n_seqs, s);
+    }
     if (dim <= 32) return launch_scan<4>(p, n_seqs, s);
     if (dim <= 64) return launch_scan<8>(p, n_seqs, s);
     if (dim <= 128) return launch_scan<16>(p, n_seqs, s);
@@ -796,16 +899,16 @@ static int launch_chunk_scan(const ChunkScanParams& p, int n_seqs, cudaStream_t 
     return QT_OK;
 }
 
-template <int RQ>
+template <int LPC, int RQ>
 static int launch_chunk_scan_fast(const ChunkScanParams& p, int n_seqs, cudaStream_t s) {
-    const size_t smem = 2 * ((size_t)CH * (3 * 64 * RQ + AB + FAST_COLS) + 64 * RQ) * sizeof(float);
+    const size_t smem = 2 * ((size_t)CH * (3 * 4 * LPC * RQ + AB + FAST_COLS) + 4 * LPC * RQ) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(delta_chunk_scan_fast_kernel<RQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+        cudaError_t err = cudaFuncSetAttribute(delta_chunk_scan_fast_kernel<LPC, RQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "delta_chunk_scan: cannot raise shared memory: %s", cudaGetErrorString(err));
         configured = true;
     }
-    launch_kernel(delta_chunk_scan_fast_kernel<RQ>, dim3(p.vdim / FAST_COLS, p.heads, n_seqs), dim3(FAST_COLS * CH), smem, s, p);
+    launch_kernel(delta_chunk_scan_fast_kernel<LPC, RQ>, dim3(p.vdim / FAST_COLS, p.heads, n_seqs), dim3(FAST_COLS * LPC), smem, s, p);
     QT_CHECK_LAUNCH("delta_chunk_scan");
     return QT_OK;
 }
@@ -836,10 +939,12 @@ extern "C" int qt_delta_scan_chunked(const float* q, const float* k, const float
     const bool aligned = ((uintptr_t)kt % 16 == 0) && ((uintptr_t)qt % 16 == 0) && ((uintptr_t)kb % 16 == 0) && ((uintptr_t)gc % 16 == 0) &&
                          ((uintptr_t)ab % 16 == 0) && ((uintptr_t)v % 16 == 0);
     if (!plain_only && aligned && dim % 64 == 0 && dim <= 256 && vdim % FAST_COLS == 0) {
-        if (dim == 64) return launch_chunk_scan_fast<1>(sp, n_seqs, s);
-        if (dim == 128) return launch_chunk_scan_fast<2>(sp, n_seqs, s);
-        if (dim == 192) return launch_chunk_scan_fast<3>(sp, n_seqs, s);
-        return launch_chunk_scan_fast<4>(sp, n_seqs, s);
+        // 16 lanes per column unless QT_B200_DELTA_LANES=32: a warp per column measured 3 to 7 % slower in a prefill of 2,048 tokens
+        static const bool half_warps = [] { const char* env = getenv("QT_B200_DELTA_LANES"); return !(env && env[0] == '3' && env[1] == '2'); }();
+        if (dim == 64) return launch_chunk_scan_fast<16, 1>(sp, n_seqs, s);
+        if (dim == 128) return half_warps ? launch_chunk_scan_fast<16, 2>(sp, n_seqs, s) : launch_chunk_scan_fast<32, 1>(sp, n_seqs, s);
+        if (dim == 192) return launch_chunk_scan_fast<16, 3>(sp, n_seqs, s);
+        return half_warps ? launch_chunk_scan_fast<16, 4>(sp, n_seqs, s) : launch_chunk_scan_fast<32, 2>(sp, n_seqs, s);
     }
     if (dim <= 32) return launch_chunk_scan<4>(sp, n_seqs, s);
     if (dim <= 64) return launch_chunk_scan<8>(sp, n_seqs, s);

@@ -259,7 +259,7 @@ __global__ void expert_combine_kernel(const T* __restrict__ y, const int* __rest
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k)
             acc += to_float(y[(size_t)pair_row[t * top + k] * width + c]) * (pair_weights ? pair_weights[(size_t)t * top + k] : 1.f);
@@ -345,7 +345,9 @@ extern "C" int qt_experts_combine(const void* y, int dtype, const int* pair_row,
     if (n_tokens == 0) return QT_OK;
     cudaStream_t s = (cudaStream_t)stream;
     return QT_DISPATCH_DTYPE(dtype, "experts_combine", {
-        launch_kernel(expert_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, s, (const T*)y, pair_row, out, top, width, pair_weight, pair_weights, base,
+        // few tokens: the columns of a row over several blocks, so that the launch fills the machine
+        const unsigned column_blocks = n_tokens >= 1024 ? 1u : (unsigned)((width + 255) / 256);
+        launch_kernel(expert_combine_kernel<T>, dim3(n_tokens, column_blocks), dim3(256), 0, s, (const T*)y, pair_row, out, top, width, pair_weight, pair_weights, base,
                       base_splits, (size_t)base_stride, row_scale);
         QT_CHECK_LAUNCH("expert_combine");
         return QT_OK;
