@@ -40,6 +40,7 @@ __device__ __forceinline__ float sigmoidf(float z) { return 1.f / (1.f + expf(-z
 
 // The sum of split-K partial sums in their order, eight loads in flight at a time.
 __device__ __forceinline__ float sum_splits(const float* __restrict__ base, size_t index, int n_splits, size_t split_stride) {
+    if (n_splits == 1) return base[index];
     float acc = 0.f;
     for (int s0 = 0; s0 < n_splits; s0 += 8) {
         float v[8];
@@ -144,12 +145,12 @@ __global__ void __launch_bounds__(256) lowrank_kernel(const float* __restrict__ 
                                                       int n_tokens, int n_out) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float xs[];                                 // [LR_TOKENS][rank]
+    extern __shared__ __align__(16) float xs[];                   // [rank][LR_TOKENS]: a column's 16 tokens side by side
     const int t0 = blockIdx.y * LR_TOKENS;
     const int count = min(LR_TOKENS, n_tokens - t0);
     for (int i = threadIdx.x; i < LR_TOKENS * rank; i += blockDim.x) {
         const int tt = i / rank, r = i % rank;
-        xs[i] = tt < count ? sum_splits(proj, (size_t)(t0 + tt) * proj_cols + x_offset + r, n_splits, split_stride) : 0.f;
+        xs[r * LR_TOKENS + tt] = tt < count ? sum_splits(proj, (size_t)(t0 + tt) * proj_cols + x_offset + r, n_splits, split_stride) : 0.f;
     }
     __syncthreads();
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
@@ -164,8 +165,12 @@ __global__ void __launch_bounds__(256) lowrank_kernel(const float* __restrict__ 
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             if (r0 + j < rank) {
+                const float4* x4 = reinterpret_cast<const float4*>(xs + (r0 + j) * LR_TOKENS);
 #pragma unroll
-                for (int tt = 0; tt < LR_TOKENS; ++tt) acc[tt] += wv[j] * xs[tt * rank + r0 + j];
+                for (int q = 0; q < LR_TOKENS / 4; ++q) {
+                    const float4 x = x4[q];
+                    acc[4 * q] += wv[j] * x.x; acc[4 * q + 1] += wv[j] * x.y; acc[4 * q + 2] += wv[j] * x.z; acc[4 * q + 3] += wv[j] * x.w;
+                }
             }
         }
     }
