@@ -531,6 +531,30 @@ def test_unequal_batches_with_slots_and_pages_used_again(name, dtype):
     engine.check_kernels()
 
 
+@pytest.mark.parametrize("name, dtype", [("vunepel-tiny-a", "fp32"), ("vunepel-tiny-a", "bf16"), ("vunepel-tiny-b", "bf16"), ("odd", "fp32")])
+def test_many_short_requests_at_once(name, dtype):
+    """Twenty-one requests of 1 to 41 tokens start together and are decoded together for six steps: more rows than the
+    cluster-fused products take, a captured step padded to 32 rows, experts in tiles, and every request against its
+    own run."""
+    engine = engine_of(name, dtype, peaky=True)
+    requests = [tokens_of(name, 1 + 2 * i + 6, 100 + i) for i in range(21)]
+    slots = [engine.new_sequence() for _ in requests]
+    logits = engine.step([StepEntry(slot, req[:-6], list(range(len(req) - 6))) for slot, req in zip(slots, requests)]).cpu()
+    got, at = [], 0
+    for req in requests:
+        got.append([logits[at:at + len(req) - 6]])
+        at += len(req) - 6
+    for step in range(6):
+        logits = engine.step([StepEntry(slot, [req[len(req) - 6 + step]], [0]) for slot, req in zip(slots, requests)]).cpu()
+        for i in range(len(requests)):
+            got[i].append(logits[i:i + 1])
+    for slot in slots:
+        engine.release(slot)
+    for i, req in enumerate(requests):
+        close(torch.cat(got[i]), oracle(name, dtype, True, tuple(req)), dtype, f"{name} request {i} of 21", model_rows=True)
+    engine.check_kernels()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding_of_several_rows(dtype):
     """Five rows decoded for 150 steps from short prompts: every chunk edge of the model is crossed several times and the
