@@ -275,7 +275,7 @@ class VunepelConfig:
             embedding=PartSpec("token_embedding", {"name": "embed", "init_std": 0.5}),
             layers=tuple(layers), schedule=tuple(schedule),
             final_norm=PartSpec("dynamic_tanh", {**norm_params, "name": "final.norm"}),
-            head=PartSpec("linear_head", {"name": "head", "tied_to": None}),
+            head=PartSpec("linear_head", {"name": "head", "tied_to": None, "init_std": 0.25}),
             max_positions=MAX_POSITIONS, eos_token_ids=(),
         )
         spec.validate()

@@ -50,7 +50,8 @@ class LinearHead:
     @classmethod
     def expected_tensors(cls, params, vocab_size: int, hidden_size: int) -> dict[str, TensorSpec]:
         # a tied model may still store the head; it is then read past, as in the reference
-        return {params["name"]: TensorSpec((vocab_size, hidden_size), optional=params.get("tied_to") is not None)}
+        return {params["name"]: TensorSpec((vocab_size, hidden_size), optional=params.get("tied_to") is not None,
+                                           init_std=float(params.get("init_std", 0.02)))}
 
     def load(self, source, embedding: TokenEmbedding | None = None) -> None:
         if self.tied_to is not None:
