@@ -238,7 +238,7 @@ class VunepelConfig:
         layers, schedule = [], []
         for index, layer in enumerate(self.layers):
             if layer.type == "attention":
-                position = PartSpec("rope", {"theta": layer.rot_base, "rotary_dim": layer.rot_dims, "head_dim": layer.dim}) \
+                position = PartSpec("rope", {"theta": layer.rot_base, "rotary_dim": layer.rot_dims, "head_dim": layer.dim, "angles": "float64"}) \
                     if layer.rot_dims else PartSpec("none")
                 mixer = PartSpec("attention", {
                     "hidden_size": self.width, "num_heads": layer.heads, "num_kv_heads": layer.kv_heads, "head_dim": layer.dim,

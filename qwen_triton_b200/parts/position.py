@@ -24,17 +24,24 @@ class RotaryTable:
         self.interleaved = pairing == "interleaved"
         if self.rotary_dim % 2 or self.rotary_dim <= 0 or self.rotary_dim > int(params["head_dim"]):
             raise ValueError(f"rotary_dim={self.rotary_dim} must be even and within head_dim={params['head_dim']}")
+        # "float64": frequencies and angles are formed in float64 and only cos and sin are rounded to float, so that an
+        # angle of thousands of radians is not off by its float rounding; the default forms them in float as the
+        # reference does
+        self.angles = str(params.get("angles", "float32"))
+        if self.angles not in ("float32", "float64"):
+            raise ValueError(f"rotary angles in {self.angles!r} (float32 or float64)")
         self.runtime = runtime
 
     def key(self) -> tuple:
-        return ("rope", self.theta, self.rotary_dim)          # the table does not depend on the pairing
+        return ("rope", self.theta, self.rotary_dim, self.angles)          # the table does not depend on the pairing
 
     def table(self, max_positions: int) -> torch.Tensor:
         """float32 [max_positions, rotary_dim]: cos in the first half of each row, sin in the second."""
-        exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+        work = torch.float64 if self.angles == "float64" else torch.float32
+        exponent = torch.arange(0, self.rotary_dim, 2, dtype=work) / self.rotary_dim
         inv_freq = 1.0 / (self.theta ** exponent)
-        angles = torch.arange(max_positions, dtype=torch.float32)[:, None] * inv_freq[None, :]
-        return torch.cat((angles.cos(), angles.sin()), dim=-1).contiguous().to(self.runtime.device)
+        angles = torch.arange(max_positions, dtype=work)[:, None] * inv_freq[None, :]
+        return torch.cat((angles.cos(), angles.sin()), dim=-1).to(torch.float32).contiguous().to(self.runtime.device)
 
 
 @register_position("none")
