@@ -159,6 +159,33 @@ def test_capped_gate(dtype, tokens, inter, limit):
     close(out, want, dtype, "capped gate")
 
 
+@pytest.mark.parametrize("rows", [5, 16, 100, 300, 700])
+@pytest.mark.parametrize("limit", [0.7, 4.0])
+def test_capped_gate_in_the_products_epilogues(rows, limit):
+    """The gate/up product with the capped gate in its epilogue, in each of the three kernels that have one (the
+    cluster-fused product up to 16 rows, the one-block product, the block-pair product beyond 256 rows), against the
+    plain product and gate."""
+    torch.manual_seed(rows)
+    width, inter = 192, 160
+    x = torch.randn(rows, width).to(torch.bfloat16)
+    gate, up = (torch.randn(inter, width) * 0.2).to(torch.bfloat16), (torch.randn(inter, width) * 0.2).to(torch.bfloat16)
+    want = plain.clamped_gate(x.double() @ gate.double().T, x.double() @ up.double().T, limit)
+    weight = kernels.interleave_gate_up(gate, up, kernels.SWIGLU_GROUP).to(DEV).contiguous()
+    out = torch.empty(rows, inter, dtype=torch.bfloat16, device=DEV)
+    target = GemmOut(out.view(1, rows, inter))
+    if rows > 256:
+        kernels.gemm_tc_pair(x.to(DEV), weight, target, swiglu=True, activation=kernels.CAPPED_GATE, limit=limit)
+    else:
+        kernels.gemm_tc(x.to(DEV), weight, target, swiglu=True, activation=kernels.CAPPED_GATE, limit=limit)
+    kernels.check_status(DEV)
+    close(out, want, "bf16", "the gate in the product's epilogue")
+    if rows <= 16:
+        out.zero_()
+        kernels.gemm_fused_swiglu(x.to(DEV), weight, out, splits=2, activation=kernels.CAPPED_GATE, limit=limit)
+        kernels.check_status(DEV)
+        close(out, want, "bf16", "the gate in the cluster-fused product's epilogue")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, dv, lam", [(3, 20, 0.7), (1, 130, -0.4), (8, 64, 0.05)])
 def test_two_maps_into_one_head(dtype, heads, dv, lam):
